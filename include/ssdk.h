@@ -257,9 +257,10 @@ int ssdk_verify(const void* logits_p, const void* logits_q, const int64_t* specu
 /* ---- layered ("hybrid") models ---------------------------------------------------
  * A second model family beside the dense Llama / Qwen3 decoders above: a program of layers, each one token mixer
  * (a recurrent layer, latent attention, or grouped-query attention beside a delta rule) and an optional feed-forward.
- * Two block kinds (SSDK_BLOCK_*): mixer and mixture of experts read the SAME normed input and join the residual
- * stream through per-channel layer scales (parallel pre-norm), or each sublayer reads the residual stream itself and
- * its OUTPUT is normed before it is added (serial post-norm).  The reference has no such model; these entry
+ * Three block kinds (SSDK_BLOCK_*): mixer and mixture of experts read the SAME normed input and join the residual
+ * stream through per-channel layer scales (parallel pre-norm); each sublayer reads the residual stream itself and
+ * its OUTPUT is normed before it is added (serial post-norm); or mixer and feed-forward read the same residual row
+ * through a norm weight of their own and are added unscaled (parallel, two norms).  The reference has no such model; these entry
  * points follow the conventions of the ones above (caller-owned device memory, int return codes).
  * Storage type T of weights / activations / latent cache: bf16 (fp32 accumulation; residual stream, norms, routers,
  * attention scores, gates and recurrent state in fp32) or fp32 throughout (no TF32). */
@@ -268,10 +269,14 @@ enum { SSDK_MIX_WKV = 0, SSDK_MIX_MLSTM = 1, SSDK_MIX_LATENT_ATTN = 2,
        SSDK_MIX_RGLRU = 3,        /* gated diagonal linear recurrence behind a short convolution, times a gelu branch */
        SSDK_MIX_SELECTIVE = 4,    /* selective scan (input-dependent step, B, C) behind a short convolution, silu gate */
        SSDK_MIX_ATTN_DELTA = 5 }; /* grouped-query sink attention and a gated delta rule side by side on the same input */
-enum { SSDK_MLP_NONE = 0, SSDK_MLP_MOE = 1, SSDK_MLP_GLU = 2 /* dense: down(gelu_tanh(gate h) * (up h)) */ };
+enum { SSDK_MLP_NONE = 0, SSDK_MLP_MOE = 1, SSDK_MLP_GLU = 2, /* dense: down(gelu_tanh(gate h) * (up h)) */
+       SSDK_MLP_FFN = 3 };        /* dense, not gated: down(act(up h + b_up)) + b_down, act = ff_act */
+/* activations of the feed-forward kernels; CLAMPED is the limited GLU g sigmoid(1.702 g) (u + 1) */
+enum { SSDK_ACT_CLAMPED = 0, SSDK_ACT_SILU = 1, SSDK_ACT_GELU_TANH = 2, SSDK_ACT_RELU2 = 3 /* relu(z)^2 */ };
 /* how a layer joins the residual stream */
 enum { SSDK_BLOCK_PARALLEL_PRENORM = 0,  /* x += ls1 * mixer(h) + ls2 * ff(h), h = norm(x) */
-       SSDK_BLOCK_SERIAL_POSTNORM = 1 }; /* x += m * norm1(mixer(x)); x += m * norm2(ff(x)): the sublayers read x itself */
+       SSDK_BLOCK_SERIAL_POSTNORM = 1,   /* x += m * norm1(mixer(x)); x += m * norm2(ff(x)): the sublayers read x itself */
+       SSDK_BLOCK_PARALLEL_TWO_NORMS = 2 }; /* x += mixer(norm1(x)) + ff(norm2(x)): one statistic, two weights, no layer scales */
 
 /* tensors of a hybrid model (ssdk_hyb_bind); [out, in] row-major, storage type T */
 enum {
@@ -303,13 +308,13 @@ enum {
   SSDK_HT_MIX_NORM,      /* [H V] channel weight after the per-head unit RMS (wkv, mlstm) */
   SSDK_HT_MIX_OUT,       /* [width, H V] */
   /* mixture of experts */
-  SSDK_HT_ROUTER,        /* [E, width] */
+  SSDK_HT_ROUTER,        /* [E + identity, width] */
   SSDK_HT_EXPERT_IN,     /* [E, 2 ff, width]: per expert gate rows then up rows */
   SSDK_HT_EXPERT_OUT,    /* [E, width, ff] */
-  SSDK_HT_SHARED_IN,     /* [2 sff + 1, width]: gate | up | shared-gate row */
+  SSDK_HT_SHARED_IN,     /* [2 sff (+ 1), width]: gate | up (| shared-gate row when shared_gate) */
   SSDK_HT_SHARED_OUT,    /* [width, sff] */
   /* serial post-norm blocks */
-  SSDK_HT_NORM2,         /* [width] norm on the feed-forward's output */
+  SSDK_HT_NORM2,         /* [width] norm on the feed-forward's output (serial blocks) or input (two-norm blocks) */
   SSDK_HT_GLU_IN,        /* [2 ff, width]: gate rows then up rows */
   SSDK_HT_GLU_OUT,       /* [width, ff] */
   /* short convolutions of the recurrent mixers */
@@ -334,6 +339,15 @@ enum {
   SSDK_HT_ATTN_OUT,      /* [width, H V] */
   SSDK_HT_DELTA_ALOG,    /* [Hd] */
   SSDK_HT_DELTA_DT_B,    /* [Hd] */
+  /* latent attention with full-rank queries (q_rank = 0): ONE stacked input projection,
+   * rows: q [H (D + R)] | dkv [kv_rank + rot_dim] (absent when kv_from >= 0) | output gate [H V] (when out_gate) */
+  SSDK_HT_LAT_IN,
+  /* dense feed-forward without a gate (SSDK_MLP_FFN) */
+  SSDK_HT_FFN_IN,        /* [ff, width] */
+  SSDK_HT_FFN_IN_B,      /* [ff] */
+  SSDK_HT_FFN_OUT,       /* [width, ff] */
+  SSDK_HT_FFN_OUT_B,     /* [width] */
+  SSDK_HT_ROUTER_BIAS,   /* [E + identity] added to the scores for the CHOICE of experts only (route_bias) */
   SSDK_HT_COUNT
 };
 
@@ -362,6 +376,19 @@ typedef struct ssdk_hyb_layer_cfg {
   /* gated delta rule of SSDK_MIX_ATTN_DELTA */
   int32_t d_heads, d_kv_heads, d_dim, d_vdim;
   float   left_scale, right_scale;   /* result = left_scale * attention + right_scale * delta rule */
+  /* latent attention variants (q_rank = 0: the queries come straight from the input, SSDK_HT_LAT_IN) */
+  int32_t rot_interleaved;           /* 0: entry i turns with i + rot_dims/2; 1: entry 2i turns with 2i + 1 */
+  int32_t kv_from;                   /* -1: the layer fills a pool of its own; j: it reads the pool of latent layer j < i */
+  int32_t out_gate;                  /* 1: the concatenated heads are multiplied by sigmoid(W_g h) before the output projection */
+  int32_t learned_sink;              /* 1: SSDK_HT_LAT_SINK joins the softmax denominator; 0: plain softmax */
+  /* router variants */
+  int32_t identity;                  /* the last `identity` router outputs are experts that return their input */
+  int32_t route_softmax;             /* scores: 0 sigmoid, 1 softmax over all router outputs */
+  int32_t route_bias;                /* 1: SSDK_HT_ROUTER_BIAS is added to the scores for the choice (not for the weights) */
+  int32_t group_best;                /* a group's score: the sum of its `group_best` best choice scores (1 or 2) */
+  int32_t route_renorm;              /* 1: the chosen scores are divided by their sum */
+  int32_t expert_act, shared_gate;   /* SSDK_ACT_CLAMPED | SSDK_ACT_SILU; 1: the shared expert is scaled by sigmoid of its gate row */
+  int32_t ff_act;                    /* SSDK_MLP_FFN: SSDK_ACT_* */
 } ssdk_hyb_layer_cfg;
 
 typedef struct ssdk_hyb_cfg {

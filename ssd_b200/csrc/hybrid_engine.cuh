@@ -36,7 +36,7 @@ struct ssdk_hyb_engine {
   // workspace carve
   int64_t ws_bytes = 0;
   float *x = nullptr, *p0 = nullptr, *p1 = nullptr, *p2 = nullptr, *mix_out = nullptr, *mix2 = nullptr;
-  void *h = nullptr, *mixes = nullptr, *t0 = nullptr, *t1 = nullptr;
+  void *h = nullptr, *h2 = nullptr, *mixes = nullptr, *t0 = nullptr, *t1 = nullptr;
   // latent attention: concatenated queries, one sequence's gathered keys / transposed latents, score and weight blocks
   void *qcat = nullptr, *keys = nullptr, *lat_t = nullptr, *att_p = nullptr; float* att_s = nullptr;
   size_t att_elems = 0; int w_qcat = 0, w_key = 0, w_kr = 0, w_lh = 0;
@@ -49,7 +49,7 @@ struct ssdk_hyb_engine {
   int max_tiles = 0;
   // widths of the shared buffers (elements per row)
   int w_p0 = 0, w_p1 = 0, w_p2 = 0, w_t0 = 0, w_t1 = 0, w_e = 0, w_top = 0, w_ff2 = 0, w_ff = 0, w_sff2 = 0, w_sff = 0;
-  bool any_wkv = false, any_pair = false;
+  bool any_wkv = false, any_pair = false, any_ffn = false;
   int* h_meta = nullptr;     // pinned staging of the step's integers
   // tcgen05 path of the dense bf16 products: TMA descriptors by (pointer, rows, K, box rows), split-K partials
   bool use_tc = true;
@@ -85,7 +85,8 @@ static int hyb_derive(ssdk_hyb_engine* e) {
   const ssdk_hyb_cfg& g = e->cfg;
   size_t soff = 0, crow = 0;
   auto up = [](int& a, long long b) { if (b > a) a = (int)b; };
-  for (auto& L : e->layers) {
+  for (size_t li = 0; li < e->layers.size(); ++li) {
+    HybLayer& L = e->layers[li];
     const ssdk_hyb_layer_cfg& c = L.c;
     const int H = c.heads, D = c.dim, V = c.vdim;
     if (H < 1 || D < 1) return fail("hybrid layer: heads / dim must be positive");
@@ -102,10 +103,29 @@ static int hyb_derive(ssdk_hyb_engine* e) {
       up(e->w_p0, 2LL * H * D + 2LL * H * V + 2 * H); up(e->w_p2, (long long)H * V); up(e->w_t1, (long long)H * V);
     } else if (c.mixer == SSDK_MIX_LATENT_ATTN) {
       if (c.rot_dims > c.rot_dim || (c.rot_dims & 1)) return fail("latent attention: rot dims %d of %d", c.rot_dims, c.rot_dim);
-      L.cache_row = (size_t)c.kv_rank + c.rot_dim;
-      L.cache_rows_before = crow;
-      crow += L.cache_row;
-      up(e->w_p0, (long long)c.q_rank + c.kv_rank + c.rot_dim); up(e->w_p1, (long long)H * (D + c.rot_dim));
+      if (V < 1 || c.kv_rank < 1 || c.rot_dim < 0 || c.q_rank < 0) return fail("latent attention: bad sizes");
+      if (c.q_rank > 0 && (c.kv_from >= 0 || c.out_gate)) return fail("latent attention: a shared cache and an output gate are built for full-rank queries");
+      if (c.kv_from >= 0) {
+        // the layer reads the pool of an earlier latent layer that fills its own (same row layout and rotation)
+        if ((size_t)c.kv_from >= li) return fail("latent attention: layer %d reads the cache of layer %d, which does not run before it", (int)li, c.kv_from);
+        const HybLayer& src = e->layers[c.kv_from];
+        if (src.c.mixer != SSDK_MIX_LATENT_ATTN || src.c.kv_from >= 0) return fail("latent attention: layer %d has no latent cache of its own", c.kv_from);
+        if (src.c.kv_rank != c.kv_rank || src.c.rot_dim != c.rot_dim || src.c.rot_dims != c.rot_dims || src.c.rot_base != c.rot_base ||
+            src.c.rot_interleaved != c.rot_interleaved)
+          return fail("latent attention: layers %d and %d disagree on the cached row", (int)li, c.kv_from);
+        L.cache_row = 0;
+        L.cache_rows_before = src.cache_rows_before;
+      } else {
+        L.cache_row = (size_t)c.kv_rank + c.rot_dim;
+        L.cache_rows_before = crow;
+        crow += L.cache_row;
+      }
+      if (c.q_rank > 0) {
+        up(e->w_p0, (long long)c.q_rank + c.kv_rank + c.rot_dim); up(e->w_p1, (long long)H * (D + c.rot_dim));
+      } else {
+        up(e->w_p0, (long long)H * (D + c.rot_dim) + (c.kv_from < 0 ? c.kv_rank + c.rot_dim : 0) + (c.out_gate ? (long long)H * V : 0));
+        up(e->w_p1, (long long)H * V);
+      }
       up(e->w_qcat, (long long)H * (c.kv_rank + c.rot_dim)); up(e->w_key, (long long)c.kv_rank + c.rot_dim);
       up(e->w_kr, c.kv_rank); up(e->w_lh, H);
       up(e->w_t0, std::max((long long)c.q_rank, (long long)H * c.kv_rank)); up(e->w_t1, std::max((long long)H * D, (long long)H * V));
@@ -149,13 +169,22 @@ static int hyb_derive(ssdk_hyb_engine* e) {
       if (c.ff < 1) return fail("dense feed-forward: ff %d", c.ff);
       if (e->cfg.block != SSDK_BLOCK_SERIAL_POSTNORM) return fail("the dense feed-forward is built for serial blocks");
       up(e->w_p0, 2LL * c.ff); up(e->w_t0, c.ff);
+    } else if (c.mlp == SSDK_MLP_FFN) {
+      if (c.ff < 1) return fail("dense feed-forward: ff %d", c.ff);
+      if (e->cfg.block == SSDK_BLOCK_SERIAL_POSTNORM) return fail("the ungated feed-forward is built for parallel blocks");
+      if (c.ff_act != SSDK_ACT_RELU2 && c.ff_act != SSDK_ACT_GELU_TANH && c.ff_act != SSDK_ACT_SILU) return fail("dense feed-forward: unknown activation %d", c.ff_act);
+      up(e->w_sff2, c.ff); up(e->w_sff, c.ff);   // it shares the shared expert's buffers: no layer has both
+      e->any_ffn = true;
     } else if (c.mlp == SSDK_MLP_MOE) {
-      if (e->cfg.block != SSDK_BLOCK_PARALLEL_PRENORM) return fail("the mixture of experts is built for parallel blocks");
-      if (c.experts < 1 || c.experts > kRouterMaxE) return fail("moe: 1 <= experts <= %d", kRouterMaxE);
-      if (c.groups < 1 || c.experts % c.groups) return fail("moe: %d experts do not form %d equal groups", c.experts, c.groups);
+      const int Et = c.experts + c.identity;   // router outputs: real experts, then identity experts
+      if (e->cfg.block == SSDK_BLOCK_SERIAL_POSTNORM) return fail("the mixture of experts is built for parallel blocks");
+      if (c.experts < 1 || c.identity < 0 || Et > kRouterMaxE) return fail("moe: 1 <= experts (+ identity) <= %d", kRouterMaxE);
+      if (c.groups < 1 || Et % c.groups) return fail("moe: %d router outputs do not form %d equal groups", Et, c.groups);
       if (c.keep < 1 || c.keep > c.groups) return fail("moe: keep %d of %d groups", c.keep, c.groups);
-      if (c.top < 1 || c.top > 32 || c.top > c.keep * (c.experts / c.groups)) return fail("moe: top %d does not fit the kept groups", c.top);
-      up(e->w_e, c.experts); up(e->w_top, c.top); up(e->w_ff2, 2LL * c.ff); up(e->w_ff, c.ff);
+      if (c.top < 1 || c.top > 32 || c.top > c.keep * (Et / c.groups)) return fail("moe: top %d does not fit the kept groups", c.top);
+      if (c.group_best != 1 && c.group_best != 2) return fail("moe: a group scores its 1 or 2 best, not %d", c.group_best);
+      if (c.expert_act != SSDK_ACT_CLAMPED && c.expert_act != SSDK_ACT_SILU) return fail("moe: unknown expert activation %d", c.expert_act);
+      up(e->w_e, Et); up(e->w_top, c.top); up(e->w_ff2, 2LL * c.ff); up(e->w_ff, c.ff);
       if (c.shared_ff > 0) { up(e->w_sff2, 2LL * c.shared_ff + 1); up(e->w_sff, c.shared_ff); }
     } else if (c.mlp != SSDK_MLP_NONE) {
       return fail("hybrid layer: unknown feed-forward kind %d", c.mlp);
@@ -174,6 +203,7 @@ static int64_t hyb_carve(ssdk_hyb_engine* e, uint8_t* base) {
   auto take = [&](size_t bytes) { uint8_t* p = base ? base + off : nullptr; off = align_up(off + bytes, 256); return p; };
   e->x = (float*)take(cap * g.width * 4);
   e->h = take(cap * g.width * es);
+  e->h2 = take(g.block == SSDK_BLOCK_PARALLEL_TWO_NORMS ? cap * g.width * es : 0);
   e->mixes = take(e->any_wkv ? 5 * cap * g.width * es : 0);
   e->p0 = (float*)take(cap * e->w_p0 * 4);
   e->p1 = (float*)take(cap * e->w_p1 * 4);
@@ -397,23 +427,47 @@ struct HybRun {
   int latent(HybLayer& Lr) {
     const ssdk_hyb_layer_cfg& c = Lr.c;
     const int H = c.heads, D = c.dim, V = c.vdim, R = c.rot_dim, KR = c.kv_rank, QR = c.q_rank, W = e->cfg.width;
-    const int Nd = QR + KR + R;
-    CKI(check_tensor(Lr, SSDK_HT_LAT_DOWN, Nd, W, "latent.down")); CKI(check_tensor(Lr, SSDK_HT_LAT_QNORM, QR, 1, "dq.norm"));
-    CKI(check_tensor(Lr, SSDK_HT_LAT_KVNORM, KR, 1, "dkv.norm")); CKI(check_tensor(Lr, SSDK_HT_LAT_UQ, (int64_t)H * (D + R), QR, "uq"));
+    const bool own = c.kv_from < 0;   // the layer fills a pool of its own (else it reads an earlier layer's rows of this step and before)
+    const int Nq = H * (D + R), Nkv = own ? KR + R : 0;
     CKI(check_tensor(Lr, SSDK_HT_LAT_UKT, (int64_t)H * KR, D, "uk^T")); CKI(check_tensor(Lr, SSDK_HT_LAT_UV, (int64_t)H * V, KR, "uv"));
-    CKI(check_tensor(Lr, SSDK_HT_LAT_SINK, H, 1, "sink")); CKI(check_tensor(Lr, SSDK_HT_MIX_OUT, W, (int64_t)H * V, "mix.o"));
+    CKI(check_tensor(Lr, SSDK_HT_MIX_OUT, W, (int64_t)H * V, "mix.o"));
+    if (own) CKI(check_tensor(Lr, SSDK_HT_LAT_KVNORM, KR, 1, "dkv.norm"));
+    if (c.learned_sink) CKI(check_tensor(Lr, SSDK_HT_LAT_SINK, H, 1, "sink"));
     if (!e->cache) return fail("hybrid: latent cache not bound");
     uint8_t* pool = e->cache + (size_t)e->num_blocks * e->cfg.block_size * Lr.cache_rows_before * e->esz;
-    CKI(lin(e->h, W, Lr.t[SSDK_HT_LAT_DOWN].p, W, e->p0, Nd, M, Nd, W));
+    const void* sink = c.learned_sink ? Lr.t[SSDK_HT_LAT_SINK].p : nullptr;
+    const float* q = nullptr;       // fp32 query rows [H, D + R] with leading dimension ldq
+    const float* gate = nullptr;    // fp32 pre-activations of the output gate [H V], leading dimension ldq
+    int ldq = 0;
     ssdk::LatentPrepArgs pa;
-    pa.z = e->p0; pa.ldz = Nd; pa.qn_w = Lr.t[SSDK_HT_LAT_QNORM].p; pa.kvn_w = Lr.t[SSDK_HT_LAT_KVNORM].p; pa.cq = e->t0;
+    pa.qn_w = nullptr; pa.kvn_w = own ? Lr.t[SSDK_HT_LAT_KVNORM].p : nullptr; pa.cq = e->t0;
     pa.cache = pool; pa.inv_freq = Lr.inv_freq; pa.q_rank = QR; pa.kv_rank = KR; pa.rot_dim = R; pa.rot_dims = c.rot_dims;
-    pa.eps = e->cfg.eps;
-    CKI(L.go(ssdk::latent_prep_kernel<T>, dim3(M), dim3(128), 0, pa, rg));
-    CKI(lin(e->t0, QR, Lr.t[SSDK_HT_LAT_UQ].p, QR, e->p1, H * (D + R), M, H * (D + R), QR));
+    pa.interleaved = c.rot_interleaved; pa.eps = e->cfg.eps;
+    if (QR > 0) {
+      // low-rank queries: down projection (query latent | kv latent | key rot part), norms, then the query up projection
+      const int Nd = QR + KR + R;
+      CKI(check_tensor(Lr, SSDK_HT_LAT_DOWN, Nd, W, "latent.down")); CKI(check_tensor(Lr, SSDK_HT_LAT_QNORM, QR, 1, "dq.norm"));
+      CKI(check_tensor(Lr, SSDK_HT_LAT_UQ, (int64_t)Nq, QR, "uq"));
+      CKI(lin(hin, W, Lr.t[SSDK_HT_LAT_DOWN].p, W, e->p0, Nd, M, Nd, W));
+      pa.z = e->p0; pa.ldz = Nd; pa.qn_w = Lr.t[SSDK_HT_LAT_QNORM].p;
+      CKI(L.go(ssdk::latent_prep_kernel<T>, dim3(M), dim3(128), 0, pa, rg));
+      CKI(lin(e->t0, QR, Lr.t[SSDK_HT_LAT_UQ].p, QR, e->p1, Nq, M, Nq, QR));
+      q = e->p1; ldq = Nq;
+    } else {
+      // full-rank queries: ONE stacked projection q | kv latent, key rot part (own pool only) | output gate
+      const int Nin = Nq + Nkv + (c.out_gate ? H * V : 0);
+      CKI(check_tensor(Lr, SSDK_HT_LAT_IN, Nin, W, "latent.in"));
+      CKI(lin(hin, W, Lr.t[SSDK_HT_LAT_IN].p, W, e->p0, Nin, M, Nin, W));
+      q = e->p0; ldq = Nin;
+      if (c.out_gate) gate = e->p0 + Nq + Nkv;
+      if (own) {
+        pa.z = e->p0 + Nq; pa.ldz = Nin;
+        CKI(L.go(ssdk::latent_prep_kernel<T>, dim3(M), dim3(128), 0, pa, rg));
+      }
+    }
     const int Wd = KR + R;
-    CKI(L.go(ssdk::latent_q_kernel<T>, dim3(M, H), dim3(64), 0, (const float*)e->p1, (T*)e->t1, (T*)e->qcat, (const float*)Lr.inv_freq, rg,
-             H, D, R, KR, c.rot_dims));
+    CKI(L.go(ssdk::latent_q_kernel<T>, dim3(M, H), dim3(64), 0, q, ldq, (T*)e->t1, (T*)e->qcat, (const float*)Lr.inv_freq, rg,
+             H, D, R, KR, c.rot_dims, c.rot_interleaved));
     // absorption: qcat[m, h, :kv_rank] = W_uk,h^T qn[m, h, :]
     CKI(lin(e->t1, H * D, Lr.t[SSDK_HT_LAT_UKT].p, D, e->qcat, H * Wd, M, KR, D, true, H, D, (long long)KR * D, Wd));
     // single-token sequences (decode) share ONE fused launch + a merge; the others take the GEMM path below
@@ -430,7 +484,7 @@ struct HybRun {
         splits = (int)std::min<size_t>(splits, e->att_elems / per_split);
         if (splits >= 1) {
           ssdk::LatentDecodeArgs da;
-          da.qcat = e->qcat; da.cache = pool; da.sink = Lr.t[SSDK_HT_LAT_SINK].p; da.part = e->att_s; da.out = e->t0;
+          da.qcat = e->qcat; da.cache = pool; da.sink = sink; da.part = e->att_s; da.out = e->t0;
           da.H = H; da.KR = KR; da.W = Wd; da.splits = splits; da.scale = c.attn_scale; da.pool_aligned = ((uintptr_t)pool & 15) == 0;
           CKI(L.go(ssdk::latent_decode_partial_kernel<T>, dim3(rg.n_seqs, splits), dim3(ssdk::kDecThreads), smem, da, rg));
           CKI(L.go(ssdk::latent_decode_merge_kernel<T>, dim3(rg.n_seqs, H), dim3(128), 0, da, rg));
@@ -449,46 +503,79 @@ struct HybRun {
         const T* qrows = (const T*)e->qcat + (size_t)(r0 + q0) * H * Wd;
         CKI(lin(qrows, Wd, e->keys, Wd, e->att_s, cb, rows, cb, Wd, false, 1, 0, 0, 0, false));
         CKI(L.go(ssdk::sink_softmax_kernel<T>, dim3(rows), dim3(256), 0, (const float*)e->att_s, (T*)e->att_p,
-                 (const T*)Lr.t[SSDK_HT_LAT_SINK].p, H, cb, p0 + q0, c.attn_scale, rows, 0.f));
+                 (const T*)sink, H, cb, p0 + q0, c.attn_scale, rows, 0.f));
         CKI(lin(e->att_p, cb, e->lat_t, ctx_pad, (T*)e->t0 + (size_t)(r0 + q0) * H * KR, KR, rows, KR, cb, true, 1, 0, 0, 0, false));
       }
     }
-    // per-head value projection of the latent output, rounded to T for the output projection
-    CKI(lin(e->t0, H * KR, Lr.t[SSDK_HT_LAT_UV].p, KR, e->t1, H * V, M, V, KR, true, H, KR, (long long)V * KR, V));
+    // per-head value projection of the latent output, rounded to T for the output projection (after the sigmoid gate on
+    // the concatenated heads, if the layer has one: the product stays fp32 up to the gate)
+    if (gate) {
+      CKI(lin(e->t0, H * KR, Lr.t[SSDK_HT_LAT_UV].p, KR, e->p1, H * V, M, V, KR, false, H, KR, (long long)V * KR, V));
+      CKI(L.go(ssdk::attn_gate_kernel<T>, dim3(M), dim3(256), 0, (const float*)e->p1, gate, ldq, (T*)e->t1, M, H, 1, V));
+    } else {
+      CKI(lin(e->t0, H * KR, Lr.t[SSDK_HT_LAT_UV].p, KR, e->t1, H * V, M, V, KR, true, H, KR, (long long)V * KR, V));
+    }
     return lin(e->t1, H * V, Lr.t[SSDK_HT_MIX_OUT].p, H * V, e->mix_out, W, M, W, H * V);
   }
 
+  const void* fin = nullptr;   // the feed-forward's input in the storage type (the mixer's input, or the second norm's rows)
+
   int moe(HybLayer& Lr) {
     const ssdk_hyb_layer_cfg& c = Lr.c;
-    const int W = e->cfg.width, E = c.experts, ff = c.ff, top = c.top, A = M * top;
-    CKI(check_tensor(Lr, SSDK_HT_ROUTER, E, W, "router")); CKI(check_tensor(Lr, SSDK_HT_EXPERT_IN, (int64_t)E * 2 * ff, W, "experts.in"));
+    const int W = e->cfg.width, E = c.experts, Et = E + c.identity, ff = c.ff, top = c.top, A = M * top;
+    CKI(check_tensor(Lr, SSDK_HT_ROUTER, Et, W, "router")); CKI(check_tensor(Lr, SSDK_HT_EXPERT_IN, (int64_t)E * 2 * ff, W, "experts.in"));
     CKI(check_tensor(Lr, SSDK_HT_EXPERT_OUT, (int64_t)E * W, ff, "experts.out"));
-    CKI(lin(e->h, W, Lr.t[SSDK_HT_ROUTER].p, W, e->rz, E, M, E, W));
+    if (c.route_bias) CKI(check_tensor(Lr, SSDK_HT_ROUTER_BIAS, Et, 1, "router.bias"));
+    CKI(lin(fin, W, Lr.t[SSDK_HT_ROUTER].p, W, e->rz, Et, M, Et, W));
     ssdk::RouterArgs ra;
-    ra.z = e->rz; ra.sel = e->sel; ra.wts = e->wts; ra.M = M; ra.E = E; ra.top = top; ra.groups = c.groups; ra.keep = c.keep;
-    ra.route_scale = c.route_scale;
-    CKI(L.go(ssdk::group_topk_router_kernel, dim3((M + ssdk::kRouterWarps - 1) / ssdk::kRouterWarps), dim3(ssdk::kRouterWarps * 32), 0, ra));
+    ra.z = e->rz; ra.bias = c.route_bias ? Lr.t[SSDK_HT_ROUTER_BIAS].p : nullptr; ra.sel = e->sel; ra.wts = e->wts; ra.M = M; ra.E = Et;
+    ra.top = top; ra.groups = c.groups; ra.keep = c.keep; ra.softmax = c.route_softmax; ra.group_best = c.group_best;
+    ra.renorm = c.route_renorm; ra.route_scale = c.route_scale;
+    CKI(L.go(ssdk::group_topk_router_kernel<T>, dim3((M + ssdk::kRouterWarps - 1) / ssdk::kRouterWarps), dim3(ssdk::kRouterWarps * 32), 0, ra));
     ssdk::PlanArgs pa;
     pa.sel = e->sel; pa.apos = e->apos; pa.arow = e->arow; pa.tile_expert = e->tile_expert; pa.tile_row0 = e->tile_row0;
-    pa.tile_rows = e->tile_rows; pa.n_tiles = e->n_tiles; pa.n_rows = e->n_rows; pa.A = A; pa.E = E; pa.top = top; pa.tile = ssdk::kLinBM;
+    pa.tile_rows = e->tile_rows; pa.n_tiles = e->n_tiles; pa.n_rows = e->n_rows; pa.A = A; pa.E = Et; pa.top = top; pa.tile = ssdk::kLinBM;
+    pa.E_real = E;
     CKI(L.go(ssdk::expert_plan_kernel, dim3(1), dim3(1024), 0, pa));
     ssdk::LinearArgs a = {};
-    a.A = e->h; a.W = Lr.t[SSDK_HT_EXPERT_IN].p; a.C = e->eg; a.M = A; a.N = 2 * ff; a.K = W; a.lda = W; a.ldw = W; a.ldc = 2 * ff;
+    a.A = fin; a.W = Lr.t[SSDK_HT_EXPERT_IN].p; a.C = e->eg; a.M = A; a.N = 2 * ff; a.K = W; a.lda = W; a.ldw = W; a.ldc = 2 * ff;
     a.a_rows = e->arow; a.tile_expert = e->tile_expert; a.tile_row0 = e->tile_row0; a.tile_rows = e->tile_rows; a.n_tiles = e->n_tiles;
     a.sW_expert = (long long)2 * ff * W;
     CKI(lin_args<float>(a, A, 1));
-    CKI(L.go(ssdk::clamped_glu_kernel<T>, dim3(A), dim3(128), 0, (const float*)e->eg, 2 * ff, (T*)e->ey, ff, c.limit, (const int*)nullptr));
+    const int* n_real_rows = c.identity > 0 ? e->n_rows : nullptr;   // rows behind them belong to identity experts: nothing to compute
+    if (c.expert_act == SSDK_ACT_SILU)
+      CKI(L.go(ssdk::glu_act_kernel<T, SSDK_ACT_SILU>, dim3(A), dim3(128), 0, (const float*)e->eg, 2 * ff, (T*)e->ey, ff, n_real_rows));
+    else
+      CKI(L.go(ssdk::clamped_glu_kernel<T>, dim3(A), dim3(128), 0, (const float*)e->eg, 2 * ff, (T*)e->ey, ff, c.limit, n_real_rows));
     a.A = e->ey; a.W = Lr.t[SSDK_HT_EXPERT_OUT].p; a.C = e->eo; a.N = W; a.K = ff; a.lda = ff; a.ldw = ff; a.ldc = W; a.a_rows = nullptr;
     a.sW_expert = (long long)W * ff;
     CKI(lin_args<float>(a, A, 1));
     if (c.shared_ff > 0) {
-      const int sff = c.shared_ff, Ns = 2 * sff + 1;
+      const int sff = c.shared_ff, Ns = 2 * sff + (c.shared_gate ? 1 : 0);
       CKI(check_tensor(Lr, SSDK_HT_SHARED_IN, Ns, W, "shared.in")); CKI(check_tensor(Lr, SSDK_HT_SHARED_OUT, W, sff, "shared.out"));
-      CKI(lin(e->h, W, Lr.t[SSDK_HT_SHARED_IN].p, W, e->sz, Ns, M, Ns, W));
-      CKI(L.go(ssdk::clamped_glu_kernel<T>, dim3(M), dim3(128), 0, (const float*)e->sz, Ns, (T*)e->sy, sff, c.shared_limit, (const int*)nullptr));
+      CKI(lin(fin, W, Lr.t[SSDK_HT_SHARED_IN].p, W, e->sz, Ns, M, Ns, W));
+      if (c.expert_act == SSDK_ACT_SILU)
+        CKI(L.go(ssdk::glu_act_kernel<T, SSDK_ACT_SILU>, dim3(M), dim3(128), 0, (const float*)e->sz, Ns, (T*)e->sy, sff, (const int*)nullptr));
+      else
+        CKI(L.go(ssdk::clamped_glu_kernel<T>, dim3(M), dim3(128), 0, (const float*)e->sz, Ns, (T*)e->sy, sff, c.shared_limit, (const int*)nullptr));
       CKI(lin(e->sy, sff, Lr.t[SSDK_HT_SHARED_OUT].p, sff, e->so, W, M, W, sff));
     }
     return 0;
+  }
+
+  // dense feed-forward without a gate: so = W_down act(W_up h + b_up); b_down joins in the block's combine
+  int ffn(HybLayer& Lr) {
+    const int W = e->cfg.width, ff = Lr.c.ff;
+    CKI(check_tensor(Lr, SSDK_HT_FFN_IN, ff, W, "mlp.up")); CKI(check_tensor(Lr, SSDK_HT_FFN_OUT, W, ff, "mlp.down"));
+    const T* b_up = (const T*)Lr.t[SSDK_HT_FFN_IN_B].p;
+    if (b_up) CKI(check_tensor(Lr, SSDK_HT_FFN_IN_B, ff, 1, "mlp.up.b"));
+    if (Lr.t[SSDK_HT_FFN_OUT_B].p) CKI(check_tensor(Lr, SSDK_HT_FFN_OUT_B, W, 1, "mlp.down.b"));
+    CKI(lin(fin, W, Lr.t[SSDK_HT_FFN_IN].p, W, e->sz, ff, M, ff, W));
+    const dim3 grid(M), block(256);
+    if (Lr.c.ff_act == SSDK_ACT_RELU2) CKI(L.go(ssdk::bias_act_kernel<T, SSDK_ACT_RELU2>, grid, block, 0, (const float*)e->sz, b_up, (T*)e->sy, ff));
+    else if (Lr.c.ff_act == SSDK_ACT_SILU) CKI(L.go(ssdk::bias_act_kernel<T, SSDK_ACT_SILU>, grid, block, 0, (const float*)e->sz, b_up, (T*)e->sy, ff));
+    else CKI(L.go(ssdk::bias_act_kernel<T, SSDK_ACT_GELU_TANH>, grid, block, 0, (const float*)e->sz, b_up, (T*)e->sy, ff));
+    return lin(e->sy, ff, Lr.t[SSDK_HT_FFN_OUT].p, ff, e->so, W, M, W, ff);
   }
 
   // ---- mixers of the serial post-norm designs (usable in either block kind: they read `hin`) ----
@@ -500,7 +587,7 @@ struct HybRun {
     const int W = e->cfg.width, ff = Lr.c.ff;
     CKI(check_tensor(Lr, SSDK_HT_GLU_IN, 2 * ff, W, "mlp.gate|up")); CKI(check_tensor(Lr, SSDK_HT_GLU_OUT, W, ff, "mlp.down"));
     CKI(lin(hin, W, Lr.t[SSDK_HT_GLU_IN].p, W, e->p0, 2 * ff, M, 2 * ff, W));
-    CKI(L.go(ssdk::glu_act_kernel<T>, dim3(M), dim3(256), 0, (const float*)e->p0, 2 * ff, (T*)e->t0, ff));
+    CKI(L.go(ssdk::glu_act_kernel<T, SSDK_ACT_GELU_TANH>, dim3(M), dim3(256), 0, (const float*)e->p0, 2 * ff, (T*)e->t0, ff, (const int*)nullptr));
     return lin(e->t0, ff, Lr.t[SSDK_HT_GLU_OUT].p, ff, e->mix_out, W, M, W, ff);
   }
 
@@ -721,19 +808,34 @@ struct HybRun {
   int layer(HybLayer& Lr, int li) {
     if (e->cfg.block == SSDK_BLOCK_SERIAL_POSTNORM) return serial_layer(Lr);
     const int W = e->cfg.width;
+    const bool two = e->cfg.block == SSDK_BLOCK_PARALLEL_TWO_NORMS;   // norm1 feeds the mixer, norm2 the feed-forward; no layer scales
+    const bool ff2 = two && Lr.c.mlp != SSDK_MLP_NONE;
     hin = e->h;
-    CKI(check_tensor(Lr, SSDK_HT_NORM, W, 1, "norm1")); CKI(check_tensor(Lr, SSDK_HT_LS_MIX, W, 1, "ls1"));
+    fin = ff2 ? e->h2 : e->h;
+    CKI(check_tensor(Lr, SSDK_HT_NORM, W, 1, "norm1"));
+    if (!two) CKI(check_tensor(Lr, SSDK_HT_LS_MIX, W, 1, "ls1"));
+    if (ff2) CKI(check_tensor(Lr, SSDK_HT_NORM2, W, 1, "norm2"));
     CKI(L.go(ssdk::offset_rmsnorm_kernel<T>, dim3(M), dim3(256), 0, (const float*)e->x, (const T*)Lr.t[SSDK_HT_NORM].p, (T*)e->h,
-             (const int*)nullptr, W, e->cfg.eps, e->cfg.norm_offset));
+             (const int*)nullptr, W, e->cfg.eps, e->cfg.norm_offset, ff2 ? (const T*)Lr.t[SSDK_HT_NORM2].p : (const T*)nullptr,
+             ff2 ? (T*)e->h2 : (T*)nullptr));
     if (Lr.c.mixer == SSDK_MIX_ATTN_DELTA) return fail("the attention pair is built for serial blocks");
     CKI(run_mixer(Lr));
     ssdk::CombineArgs ca = {};
-    ca.x = e->x; ca.mix = e->mix_out; ca.ls1 = Lr.t[SSDK_HT_LS_MIX].p; ca.width = W;
+    ca.x = e->x; ca.mix = e->mix_out; ca.ls1 = two ? nullptr : Lr.t[SSDK_HT_LS_MIX].p; ca.width = W;
     if (Lr.c.mlp == SSDK_MLP_MOE) {
-      CKI(check_tensor(Lr, SSDK_HT_LS_MLP, W, 1, "ls2"));
+      if (!two) CKI(check_tensor(Lr, SSDK_HT_LS_MLP, W, 1, "ls2"));
       CKI(moe(Lr));
-      ca.ls2 = Lr.t[SSDK_HT_LS_MLP].p; ca.routed = e->eo; ca.apos = e->apos; ca.wts = e->wts; ca.top = Lr.c.top;
-      if (Lr.c.shared_ff > 0) { ca.shared = e->so; ca.sg = e->sz + 2 * Lr.c.shared_ff; ca.ld_sg = 2 * Lr.c.shared_ff + 1; }
+      ca.ls2 = two ? nullptr : Lr.t[SSDK_HT_LS_MLP].p; ca.routed = e->eo; ca.apos = e->apos; ca.wts = e->wts; ca.top = Lr.c.top;
+      if (Lr.c.identity > 0) { ca.sel = e->sel; ca.n_real = Lr.c.experts; ca.fin = fin; }
+      if (Lr.c.shared_ff > 0) {
+        ca.shared = e->so;
+        if (Lr.c.shared_gate) { ca.sg = e->sz + 2 * Lr.c.shared_ff; ca.ld_sg = 2 * Lr.c.shared_ff + 1; }
+      }
+    } else if (Lr.c.mlp == SSDK_MLP_FFN) {
+      CKI(ffn(Lr));
+      ca.shared = e->so; ca.ff_bias = Lr.t[SSDK_HT_FFN_OUT_B].p;
+    } else if (Lr.c.mlp != SSDK_MLP_NONE) {
+      return fail("the gated dense feed-forward is built for serial blocks");
     }
     return L.go(ssdk::block_combine_kernel<T>, dim3(M), dim3(256), 0, ca);
   }
@@ -800,7 +902,7 @@ static int hyb_forward_t(ssdk_hyb_engine* e, int n_seqs, int M, const int32_t* i
   }
   if (n_want > 0) {
     CKI(run.L.go(ssdk::offset_rmsnorm_kernel<T>, dim3(n_want), dim3(256), 0, (const float*)e->x, (const T*)e->final_norm.p, (T*)e->hn,
-                 (const int*)(d + o_want), g.width, g.eps, g.norm_offset));
+                 (const int*)(d + o_want), g.width, g.eps, g.norm_offset, (const T*)nullptr, (T*)nullptr));
     CKI(run.lin(e->hn, g.width, e->head.p, g.width, e->logits, g.vocab, n_want, g.vocab, g.width));
     if (logits_host) CK(cudaMemcpyAsync(logits_host, e->logits, (size_t)n_want * g.vocab * 4, cudaMemcpyDeviceToHost, st));
     if (temps && out_tokens) {
@@ -832,7 +934,7 @@ int ssdk_hyb_create(const ssdk_hyb_cfg* cfg, const ssdk_hyb_layer_cfg* layers, s
   if (!cfg || !layers || !out) return fail("ssdk_hyb_create: null argument");
   if (cfg->width < 1 || cfg->vocab < 1 || cfg->n_layers < 1) return fail("ssdk_hyb_create: bad sizes");
   if (cfg->dtype != SSDK_DT_F32 && cfg->dtype != SSDK_DT_BF16) return fail("ssdk_hyb_create: unknown dtype %d", cfg->dtype);
-  if (cfg->block != SSDK_BLOCK_PARALLEL_PRENORM && cfg->block != SSDK_BLOCK_SERIAL_POSTNORM) return fail("ssdk_hyb_create: unknown block kind %d", cfg->block);
+  if (cfg->block != SSDK_BLOCK_PARALLEL_PRENORM && cfg->block != SSDK_BLOCK_SERIAL_POSTNORM && cfg->block != SSDK_BLOCK_PARALLEL_TWO_NORMS) return fail("ssdk_hyb_create: unknown block kind %d", cfg->block);
   if (cfg->max_tokens < 1 || cfg->max_seqs < 1 || cfg->max_logit_rows < 1 || cfg->block_size < 1 || cfg->max_blocks_per_seq < 1)
     return fail("ssdk_hyb_create: bad runtime limits");
   int ndev = 0;

@@ -1,4 +1,4 @@
-// latent_attention.cuh — attention over a compressed (latent) KV cache with a learned softmax sink.
+// latent_attention.cuh — attention over a compressed (latent) KV cache, with or without a learned softmax sink.
 //
 // What is cached per token and layer is one row [kv_rank + rot_dim] of storage type T in a paged pool: the RMS-normed
 // latent c and the ONE rotated key part shared by all heads.  Keys and values are never materialised: with
@@ -7,8 +7,9 @@
 // runs multi-query style over the latent rows (every head reads the same row), and the per-head value projection is
 // applied to the attention's latent output (a per-head GEMM against W_uv).
 //
-//   latent_prep_kernel   splits the fused down-projection: RMS-norm -> query latent (T); RMS-norm -> c and
-//                        rotate-half RoPE (fp32 angles) -> rotated key part, both scattered into the page slot
+//   latent_prep_kernel   splits the fused down-projection: RMS-norm -> query latent (T; skipped when the queries are
+//                        full-rank); RMS-norm -> c and RoPE (fp32 angles; rotate-half or interleaved pairs) -> rotated
+//                        key part, both scattered into the page slot.  A layer that reads another layer's pool skips it.
 //   latent_q_kernel      per head: unrotated query part -> T (operand of the absorption GEMM), rotated part -> RoPE;
 //                        absorbed and rotated parts share one row [kv_rank + rot_dim] per (token, head)
 //   attention proper     per sequence and query block, as two tensor-core GEMMs around a softmax (HybRun::latent):
@@ -38,8 +39,21 @@ struct LatentPrepArgs {
   void* cache;        // [rows, kv_rank + rot_dim] T (this layer's pool)
   const float* inv_freq;  // [rot_dims / 2]
   int q_rank, kv_rank, rot_dim, rot_dims;
+  int interleaved;    // 0: entry i turns with entry i + rot_dims/2; 1: entry 2i with entry 2i + 1
   float eps;
 };
+
+// entry c of a rotated vector zr at position pos: (u, v) -> (u cos a - v sin a, v cos a + u sin a), a = pos * f_i
+SSDK_DEVINL float rope_entry(const float* zr, int c, int rot_dims, int interleaved, int pos, const float* inv_freq) {
+  if (c >= rot_dims) return zr[c];
+  const int half = rot_dims / 2;
+  const bool first = interleaved ? !(c & 1) : c < half;
+  const int i = interleaved ? c >> 1 : (first ? c : c - half);
+  const int other = interleaved ? (c ^ 1) : (first ? c + half : c - half);
+  float sn, cs;
+  sincosf((float)pos * inv_freq[i], &sn, &cs);
+  return first ? zr[c] * cs - zr[other] * sn : zr[c] * cs + zr[other] * sn;
+}
 
 template <typename T>
 __global__ void latent_prep_kernel(const LatentPrepArgs p, const Ragged rg) {
@@ -47,12 +61,14 @@ __global__ void latent_prep_kernel(const LatentPrepArgs p, const Ragged rg) {
   const int m = blockIdx.x, s = rg.tok_seq[m];
   const int pos = rg.pos0[s] + (m - rg.cu[s]);
   const float* z = p.z + (size_t)m * p.ldz;
-  float ss = 0.f;
-  for (int c = threadIdx.x; c < p.q_rank; c += blockDim.x) ss = fmaf(z[c], z[c], ss);
-  ss = block_sum(ss, red);
-  float inv = 1.0f / sqrtf(ss / (float)p.q_rank + p.eps);
-  for (int c = threadIdx.x; c < p.q_rank; c += blockDim.x)
-    st_f<T>((T*)p.cq + (size_t)m * p.q_rank + c, z[c] * inv * ld_f<T>((const T*)p.qn_w + c));
+  float ss = 0.f, inv;
+  if (p.q_rank > 0) {
+    for (int c = threadIdx.x; c < p.q_rank; c += blockDim.x) ss = fmaf(z[c], z[c], ss);
+    ss = block_sum(ss, red);
+    inv = 1.0f / sqrtf(ss / (float)p.q_rank + p.eps);
+    for (int c = threadIdx.x; c < p.q_rank; c += blockDim.x)
+      st_f<T>((T*)p.cq + (size_t)m * p.q_rank + c, z[c] * inv * ld_f<T>((const T*)p.qn_w + c));
+  }
   const float* zk = z + p.q_rank;
   ss = 0.f;
   for (int c = threadIdx.x; c < p.kv_rank; c += blockDim.x) ss = fmaf(zk[c], zk[c], ss);
@@ -61,40 +77,23 @@ __global__ void latent_prep_kernel(const LatentPrepArgs p, const Ragged rg) {
   T* row = (T*)p.cache + page_row(rg, s, pos) * (size_t)(p.kv_rank + p.rot_dim);
   for (int c = threadIdx.x; c < p.kv_rank; c += blockDim.x) st_f<T>(row + c, zk[c] * inv * ld_f<T>((const T*)p.kvn_w + c));
   const float* zr = zk + p.kv_rank;
-  const int half = p.rot_dims / 2;
-  for (int c = threadIdx.x; c < p.rot_dim; c += blockDim.x) {
-    float out = zr[c];
-    if (c < p.rot_dims) {
-      const int i = c < half ? c : c - half;
-      float sn, cs;
-      sincosf((float)pos * p.inv_freq[i], &sn, &cs);
-      out = c < half ? zr[c] * cs - zr[c + half] * sn : zr[c] * cs + zr[c - half] * sn;
-    }
-    st_f<T>(row + p.kv_rank + c, out);
-  }
+  for (int c = threadIdx.x; c < p.rot_dim; c += blockDim.x)
+    st_f<T>(row + p.kv_rank + c, rope_entry(zr, c, p.rot_dims, p.interleaved, pos, p.inv_freq));
 }
 
-// q [M, H, D + R] fp32 -> qn [M, H, D] (T, operand of the absorption GEMM) and the rotated part (T) into columns
-// [kv_rank, kv_rank + R) of the concatenated query rows qcat [M, H, kv_rank + R]; the absorption GEMM fills the rest
+// q rows [ldq] fp32 holding [H, D + R] -> qn [M, H, D] (T, operand of the absorption GEMM) and the rotated part (T) into
+// columns [kv_rank, kv_rank + R) of the concatenated query rows qcat [M, H, kv_rank + R]; the absorption GEMM fills the rest
 template <typename T>
-__global__ void latent_q_kernel(const float* __restrict__ q, T* __restrict__ qn, T* __restrict__ qcat,
-                                const float* __restrict__ inv_freq, const Ragged rg, int H, int D, int R, int KR, int rot_dims) {
+__global__ void latent_q_kernel(const float* __restrict__ q, int ldq, T* __restrict__ qn, T* __restrict__ qcat,
+                                const float* __restrict__ inv_freq, const Ragged rg, int H, int D, int R, int KR, int rot_dims,
+                                int interleaved) {
   const int m = blockIdx.x, hd = blockIdx.y, s = rg.tok_seq[m];
   const int pos = rg.pos0[s] + (m - rg.cu[s]);
-  const float* src = q + ((size_t)m * H + hd) * (D + R);
+  const float* src = q + (size_t)m * ldq + (size_t)hd * (D + R);
   for (int c = threadIdx.x; c < D; c += blockDim.x) st_f<T>(qn + ((size_t)m * H + hd) * D + c, src[c]);
   const float* zr = src + D;
-  const int half = rot_dims / 2;
-  for (int c = threadIdx.x; c < R; c += blockDim.x) {
-    float out = zr[c];
-    if (c < rot_dims) {
-      const int i = c < half ? c : c - half;
-      float sn, cs;
-      sincosf((float)pos * inv_freq[i], &sn, &cs);
-      out = c < half ? zr[c] * cs - zr[c + half] * sn : zr[c] * cs + zr[c - half] * sn;
-    }
-    st_f<T>(qcat + ((size_t)m * H + hd) * (KR + R) + KR + c, out);
-  }
+  for (int c = threadIdx.x; c < R; c += blockDim.x)
+    st_f<T>(qcat + ((size_t)m * H + hd) * (KR + R) + KR + c, rope_entry(zr, c, rot_dims, interleaved, pos, inv_freq));
 }
 
 // One sequence's cached rows, made contiguous for the two attention GEMMs: keys [ctx_pad, W] (W = kv_rank + R) and the
@@ -144,7 +143,7 @@ __global__ void sink_softmax_kernel(const float* __restrict__ sc, T* __restrict_
 struct LatentDecodeArgs {
   const void* qcat;   // [M, H, W] T: latent-space query | rotated part
   const void* cache;  // [rows, W] T (this layer's pool)
-  const void* sink;   // [H] T
+  const void* sink;   // [H] T, or nullptr: plain softmax
   float* part;        // [n_seqs, splits, H, KR + 2] fp32: unnormalised P C | running maximum | running sum
   void* out;          // [M, H, KR] T
   int H, KR, W, splits;
@@ -292,7 +291,7 @@ __global__ void latent_decode_merge_kernel(const LatentDecodeArgs p, const Ragge
   const int KR = p.KR;
   const float* part = p.part + ((size_t)s * p.splits * p.H + h) * (KR + 2);
   const size_t js = (size_t)p.H * (KR + 2);  // floats between two splits of one head
-  const float sk = ld_f<T>((const T*)p.sink + h);
+  const float sk = p.sink ? ld_f<T>((const T*)p.sink + h) : -INFINITY;
   float m = sk;
   for (int j = 0; j < p.splits; ++j) m = fmaxf(m, part[j * js + KR]);
   float den = expf(sk - m);

@@ -1,14 +1,18 @@
 // layer_ops.cuh — the element-wise steps of a layered (hybrid) model's block.  The residual stream, every norm
 // statistic and every gate are fp32; T (bf16 or float) is the storage type of the activations that feed a linear layer.
 //   embed_rows_kernel         x = embed[token] * scale                          (fp32 residual; optional T copy)
-//   offset_rmsnorm_kernel     y = x / sqrt(mean(x^2) + eps) * (offset + w)       (offset 1: unit-offset weight, 0: plain)
+//   offset_rmsnorm_kernel     y = x / sqrt(mean(x^2) + eps) * (offset + w)       (offset 1: unit-offset weight, 0: plain);
+//                             optionally a second output with a second weight from the same statistic (two-norm blocks)
 //   postnorm_residual_kernel  x += mult * norm(s1 y1 + s2 y2): the norm sits on a sublayer's OUTPUT (serial blocks)
-//   glu_act_kernel            y = gelu_tanh(g) * u
+//   glu_act_kernel            y = act(g) * u, act = gelu_tanh | silu
+//   bias_act_kernel           y = act(z + b), act = relu^2 | gelu_tanh | silu     (feed-forward without a gate)
 //   token_shift_kernel        RWKV token shift: S mixes h + (h_prev - h) * mu_s, h_prev carried in the state slot
 //   head_rmsnorm_gate_kernel  per-head unit RMS, times a channel weight, times silu / sigmoid of a gate pre-activation
 //   clamped_glu_kernel        y = g * sigmoid(1.702 g) * (u + 1) with g = min(g, lim), u = clamp(u, -lim, lim)
 //   unary_kernel              tanh (decay low-rank bottleneck)
-//   block_combine_kernel      parallel block: x += ls1 * mixer + ls2 * (sum_k w_k expert_k + sigmoid(sg) * shared)
+//   block_combine_kernel      parallel block: x += ls1 * mixer + ls2 * (sum_k w_k expert_k + sigmoid(sg) * shared + b);
+//                             ls1, ls2, sg, b are optional (1, 1, no gate, 0); an identity expert's output is the
+//                             feed-forward's input row itself
 #pragma once
 #include "common.cuh"
 #include "linear.cuh"
@@ -38,10 +42,12 @@ __global__ void embed_rows_kernel(const int* __restrict__ ids, const T* __restri
   }
 }
 
-// rows: optional gather (row r of the output reads x[rows[r]])
+// rows: optional gather (row r of the output reads x[rows[r]]).  w2 / y2 (optional): a second norm of the same row
+// with its own weight — the statistic is shared, so a block whose mixer and feed-forward each have a norm reads x once.
 template <typename T>
 __global__ void offset_rmsnorm_kernel(const float* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
-                                      const int* __restrict__ rows, int width, float eps, float offset) {
+                                      const int* __restrict__ rows, int width, float eps, float offset,
+                                      const T* __restrict__ w2, T* __restrict__ y2) {
   __shared__ float red[33];
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
@@ -49,8 +55,11 @@ __global__ void offset_rmsnorm_kernel(const float* __restrict__ x, const T* __re
   for (int c = threadIdx.x; c < width; c += blockDim.x) { const float v = xr[c]; ss = fmaf(v, v, ss); }
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)width + eps);
-  for (int c = threadIdx.x; c < width; c += blockDim.x)
-    st_f<T>(y + (size_t)r * width + c, xr[c] * inv * (offset + ld_f<T>(w + c)));
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = xr[c] * inv;
+    st_f<T>(y + (size_t)r * width + c, v * (offset + ld_f<T>(w + c)));
+    if (y2) st_f<T>(y2 + (size_t)r * width + c, v * (offset + ld_f<T>(w2 + c)));
+  }
 }
 
 // Serial post-norm block: x[m] += mult * (y / sqrt(mean(y^2) + eps)) * (offset + w) with y = s1 y1[m] (+ s2 y2[m]); the
@@ -76,15 +85,33 @@ __global__ void postnorm_residual_kernel(float* __restrict__ x, const float* __r
   }
 }
 
-// z [rows, ldz] fp32 with gate columns [0, ff) and up columns [ff, 2 ff) -> y [rows, ff] (T) = gelu_tanh(gate) * up
-template <typename T>
-__global__ void glu_act_kernel(const float* __restrict__ z, int ldz, T* __restrict__ y, int ff) {
+SSDK_DEVINL float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// ACT: the SSDK_ACT_* values of the C ABI (1 silu, 2 gelu_tanh, 3 squared relu)
+template <int ACT>
+SSDK_DEVINL float act_f(float g) {
+  if (ACT == 1) return g * sigmoid_f(g);
+  if (ACT == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  const float r = fmaxf(g, 0.f);
+  return r * r;
+}
+
+// z [rows, ldz] fp32 with gate columns [0, ff) and up columns [ff, 2 ff) -> y [rows, ff] (T) = act(gate) * up; rows at
+// and beyond *n_rows (optional, on the device) are skipped
+template <typename T, int ACT>
+__global__ void glu_act_kernel(const float* __restrict__ z, int ldz, T* __restrict__ y, int ff, const int* __restrict__ n_rows) {
   const int r = blockIdx.x;
-  for (int c = threadIdx.x; c < ff; c += blockDim.x) {
-    const float g = z[(size_t)r * ldz + c];
-    const float a = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
-    st_f<T>(y + (size_t)r * ff + c, a * z[(size_t)r * ldz + ff + c]);
-  }
+  if (n_rows && r >= *n_rows) return;
+  for (int c = threadIdx.x; c < ff; c += blockDim.x)
+    st_f<T>(y + (size_t)r * ff + c, act_f<ACT>(z[(size_t)r * ldz + c]) * z[(size_t)r * ldz + ff + c]);
+}
+
+// z [rows, ff] fp32, b [ff] (T, optional) -> y [rows, ff] (T) = act(z + b)
+template <typename T, int ACT>
+__global__ void bias_act_kernel(const float* __restrict__ z, const T* __restrict__ b, T* __restrict__ y, int ff) {
+  const int r = blockIdx.x;
+  for (int c = threadIdx.x; c < ff; c += blockDim.x)
+    st_f<T>(y + (size_t)r * ff + c, act_f<ACT>(z[(size_t)r * ff + c] + (b ? ld_f<T>(b + c) : 0.f)));
 }
 
 // mixes[s][m][c] = h[m][c] + (prev[m][c] - h[m][c]) * mu[s][c]; prev of a portion's first row comes from the slot
@@ -104,8 +131,6 @@ __global__ void token_shift_kernel(const T* __restrict__ h, const T* __restrict_
       st_f<T>(mixes + ((size_t)k * rg.M + m) * width + c, fmaf(d, ld_f<T>(mu + (size_t)k * width + c), cur));
   }
 }
-
-SSDK_DEVINL float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 
 // o [M, H, V] fp32 -> y [M, H*V] (T): o / rms(o) * w * act(g);  GATE: 0 = silu, 1 = sigmoid
 template <typename T, int GATE>
@@ -161,30 +186,40 @@ __global__ void splitk_sum_kernel(const float* __restrict__ partials, float* __r
 struct CombineArgs {
   float* x;              // [M, width] residual, updated in place
   const float* mix;      // [M, width] mixer output (after its output projection)
-  const void* ls1;       // [width] T
-  const void* ls2;       // [width] T or nullptr (no feed-forward)
+  const void* ls1;       // [width] T or nullptr (no layer scale)
+  const void* ls2;       // [width] T or nullptr (no layer scale on the feed-forward)
   const float* routed;   // [M * top, width] expert outputs in assignment order, or nullptr
   const int* apos;       // [M * top] row of (token, k) in `routed`
   const float* wts;      // [M * top] routing weights
   int top;
-  const float* shared;   // [M, width] shared expert output or nullptr
-  const float* sg;       // shared gate pre-activation: sg[m * ld_sg]
+  const float* shared;   // [M, width] output of the shared expert or of a dense feed-forward, or nullptr
+  const float* sg;       // shared gate pre-activation: sg[m * ld_sg], or nullptr (no gate)
   int ld_sg;
   int width;
+  const void* ff_bias;   // [width] T bias of the feed-forward's output, or nullptr
+  const int* sel;        // [M * top] chosen router output; outputs >= n_real are identity experts (nullptr: there are none)
+  int n_real;
+  const void* fin;       // [M, width] T the feed-forward's input (what an identity expert returns)
 };
 template <typename T>
 __global__ void block_combine_kernel(const CombineArgs p) {
   const int m = blockIdx.x;
-  const float sgate = p.shared ? sigmoid_f(p.sg[(size_t)m * p.ld_sg]) : 0.f;
+  const float sgate = (p.shared && p.sg) ? sigmoid_f(p.sg[(size_t)m * p.ld_sg]) : 1.f;
   for (int c = threadIdx.x; c < p.width; c += blockDim.x) {
-    float y = ld_f<T>((const T*)p.ls1 + c) * p.mix[(size_t)m * p.width + c];
-    if (p.ls2) {
+    float y = p.mix[(size_t)m * p.width + c];
+    if (p.ls1) y *= ld_f<T>((const T*)p.ls1 + c);
+    if (p.routed || p.shared) {
       float f = 0.f;
       if (p.routed)
-        for (int k = 0; k < p.top; ++k)
-          f = fmaf(p.wts[(size_t)m * p.top + k], p.routed[(size_t)p.apos[(size_t)m * p.top + k] * p.width + c], f);
+        for (int k = 0; k < p.top; ++k) {
+          const size_t a = (size_t)m * p.top + k;
+          const float v = (p.sel && p.sel[a] >= p.n_real) ? ld_f<T>((const T*)p.fin + (size_t)m * p.width + c)
+                                                          : p.routed[(size_t)p.apos[a] * p.width + c];
+          f = fmaf(p.wts[a], v, f);
+        }
       if (p.shared) f = fmaf(sgate, p.shared[(size_t)m * p.width + c], f);
-      y = fmaf(ld_f<T>((const T*)p.ls2 + c), f, y);
+      if (p.ff_bias) f += ld_f<T>((const T*)p.ff_bias + c);
+      y = p.ls2 ? fmaf(ld_f<T>((const T*)p.ls2 + c), f, y) : y + f;
     }
     p.x[(size_t)m * p.width + c] += y;
   }

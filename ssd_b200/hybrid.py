@@ -1,4 +1,4 @@
-"""Layered ("hybrid") models: a program of layers, each one token mixer + an optional feed-forward.  Two designs are
+"""Layered ("hybrid") models: a program of layers, each one token mixer + an optional feed-forward.  Three designs are
 served through this module, told apart by config.json's `"architecture"`:
 
     Pikavik   parallel pre-norm blocks (mixer and mixture-of-experts feed-forward read the same normed input, unit-offset
@@ -7,6 +7,11 @@ served through this module, told apart by config.json's `"architecture"`:
               embedding); mixers rglru (gated diagonal recurrence behind a short convolution), mamba1 (selective scan)
               and `parallel` (grouped-query sink attention with YaRN-scaled interleaved rotation beside a gated delta
               rule); dense gelu-GLU feed-forward
+    Lisenex   parallel blocks with two norms (x += mixer(norm1 x) + ff(norm2 x), plain norm weights, scaled embedding,
+              head tied to the embedding); latent attention with full-rank queries, interleaved rotation, plain
+              softmax, a sigmoid output gate and layers that read another layer's latent cache (`kv_from`);
+              feed-forward dense (squared relu, biases) or a mixture of silu-GLU experts behind a softmax router
+              with a selection bias, group limits, identity experts and an ungated shared expert
 
     HybridSpec     what config.json (and, for sizes it does not list, the checkpoint's tensor shapes) says
     load_hybrid_weights   safetensors -> device tensors in the packed layout libssdk's ssdk_hyb_bind expects
@@ -36,6 +41,13 @@ DESIGNS = {
                 "norm_offset": 1.0},
     "Kefurax": {"mixers": ("rglru", "mamba1", "parallel"), "mlp": ("dense",), "block": L.BLOCK_SERIAL_POSTNORM,
                 "norm_offset": 0.0},
+    # constants the design fixes, as the arguments the shared mechanisms take
+    "Lisenex": {"mixers": ("latent_attention",), "mlp": ("dense", "moe"), "block": L.BLOCK_PARALLEL_TWO_NORMS,
+                "norm_offset": 0.0, "dense": "ffn", "tied_head": True,
+                "latent": {"rot_interleaved": 1, "out_gate": 1, "learned_sink": 0},
+                "moe": {"route_softmax": 1, "route_bias": 1, "group_best": 1, "route_renorm": 0, "expert_act": L.ACT_SILU,
+                        "shared_gate": 0},
+                "ffn": {"ff_act": L.ACT_RELU2}},
 }
 RGLRU_DECAY_MULT = 8.0  # log a = -8 r softplus(lam)
 
@@ -87,16 +99,34 @@ class LayerSpec:
     d_vdim: int = 0
     left_scale: float = 1.0
     right_scale: float = 1.0
+    # latent attention variants (the defaults are Pikavik's: rotate-half, own cache, no output gate, learned sink)
+    rot_interleaved: int = 0
+    kv_from: int = -1
+    out_gate: int = 0
+    learned_sink: int = 1
+    # router / expert variants (the defaults are Pikavik's: sigmoid scores, group score = two best, renormalised weights,
+    # clamped GLU, gated shared expert)
+    identity: int = 0
+    route_softmax: int = 0
+    route_bias: int = 0
+    group_best: int = 2
+    route_renorm: int = 1
+    expert_act: int = L.ACT_CLAMPED
+    shared_gate: int = 1
+    ff_act: int = L.ACT_RELU2
 
     def cfg(self) -> L.HybLayerCfg:
-        mlp = {"moe": L.MLP_MOE, "dense": L.MLP_GLU, None: L.MLP_NONE}[self.mlp]
+        mlp = {"moe": L.MLP_MOE, "dense": L.MLP_GLU, "ffn": L.MLP_FFN, None: L.MLP_NONE}[self.mlp]
         return L.HybLayerCfg(MIXERS[self.mixer], self.heads, self.dim, self.vdim, self.rot_dim, self.rot_dims, self.kv_rank,
                              self.q_rank, self.decay_rank, self.rot_base, self.attn_scale, self.gate_cap,
                              mlp, self.experts, self.top, self.groups, self.keep,
                              self.ff, self.shared_ff, self.route_scale, self.limit, self.shared_limit,
                              self.kv_heads, self.qk_norm, self.sink, self.yarn_factor, self.yarn_original, self.yarn_fast,
                              self.yarn_slow, self.conv, self.inner, self.blocks, self.state, self.dt_rank, self.decay_mult,
-                             self.d_heads, self.d_kv_heads, self.d_dim, self.d_vdim, self.left_scale, self.right_scale)
+                             self.d_heads, self.d_kv_heads, self.d_dim, self.d_vdim, self.left_scale, self.right_scale,
+                             self.rot_interleaved, self.kv_from, self.out_gate, self.learned_sink, self.identity,
+                             self.route_softmax, self.route_bias, self.group_best, self.route_renorm, self.expert_act,
+                             self.shared_gate, self.ff_act)
 
 
 @dataclass
@@ -116,6 +146,10 @@ class HybridSpec:
     @property
     def norm_offset(self) -> float:
         return DESIGNS[self.architecture]["norm_offset"]
+
+    @property
+    def tied_head(self) -> bool:
+        return bool(DESIGNS[self.architecture].get("tied_head"))
 
     @property
     def has_cache(self) -> bool:
@@ -175,22 +209,31 @@ class HybridSpec:
                 rot = m.get("rot") or {}
                 ls.vdim, ls.rot_dim = int(m["vdim"]), int(m["rot_dim"])
                 ls.rot_dims, ls.rot_base = int(rot.get("dims", ls.rot_dim)), float(rot.get("base", 10000.0))
-                ls.kv_rank, ls.q_rank, ls.attn_scale = int(m["kv_rank"]), int(m["q_rank"]), float(m["scale"])
+                ls.kv_rank, ls.q_rank, ls.attn_scale = int(m["kv_rank"]), int(m.get("q_rank", 0)), float(m["scale"])
+                src = m.get("kv_from")
+                ls.kv_from = -1 if src is None else int(src)
+                for key, val in (design.get("latent") or {}).items():
+                    setattr(ls, key, val)
             mlp = lc.get("mlp")
             if mlp:
                 mk = mlp.get("kind", design["mlp"][0])
                 if mk not in design["mlp"]:
                     raise ValueError(f"layer {i}: unknown feed-forward kind {mk!r}")
                 if mk == "dense":
-                    ls.mlp, ls.ff = "dense", int(mlp["ff"])
+                    ls.mlp, ls.ff = design.get("dense", "dense"), int(mlp["ff"])
+                    for key, val in (design.get("ffn") or {}).items():
+                        setattr(ls, key, val)
                 else:
                     r, ex, sh = mlp["router"], mlp["expert"], mlp.get("shared")
                     g = r.get("groups") or {}
                     ls.mlp, ls.experts, ls.top = "moe", int(r["experts"]), int(r["top"])
                     ls.groups, ls.keep = int(g.get("count", 1)), int(g.get("keep", g.get("count", 1)))
-                    ls.route_scale, ls.ff, ls.limit = float(r.get("scale", 1.0)), int(ex["ff"]), float(ex["limit"])
+                    ls.route_scale, ls.ff, ls.limit = float(r.get("scale", 1.0)), int(ex["ff"]), float(ex.get("limit", 0.0))
+                    ls.identity = int(r.get("identity", 0))
                     if sh:
-                        ls.shared_ff, ls.shared_limit = int(sh["ff"]), float(sh["limit"])
+                        ls.shared_ff, ls.shared_limit = int(sh["ff"]), float(sh.get("limit", 0.0))
+                    for key, val in (design.get("moe") or {}).items():
+                        setattr(ls, key, val)
             layers.append(ls)
         return cls(width=int(cfg["width"]), vocab=int(cfg["vocab"]), eps=float(cfg["norm"]["eps"]), layers=layers,
                    architecture=arch, embed_scale=float((cfg.get("embedding") or {}).get("scale", 1.0)),
@@ -241,12 +284,18 @@ def pack_hybrid_weights(spec: HybridSpec, raw: dict[str, torch.Tensor], dtype: t
     def dev(x):
         return x.to(dtype).contiguous().to(device)
 
-    w = {"EMBED": dev(t("embed")), "HEAD": dev(t("head")), "FINAL_NORM": dev(t("final.norm")), "layers": []}
+    w = {"EMBED": dev(t("embed")), "FINAL_NORM": dev(t("final.norm")), "layers": []}
+    w["HEAD"] = w["EMBED"] if spec.tied_head else dev(t("head"))   # a tied head reads the table itself (without its scale)
+    two_norms = spec.block == L.BLOCK_PARALLEL_TWO_NORMS
     for i, ls in enumerate(spec.layers):
         p, mx = f"l{i}.", f"l{i}.mix."
         lw = {"NORM": dev(t(p + "norm1"))}
         if ls.mixer in ("wkv", "mlstm", "latent_attention"):
-            lw["LS_MIX"], lw["MIX_OUT"] = dev(t(p + "ls1")), dev(t(mx + "o"))
+            lw["MIX_OUT"] = dev(t(mx + "o"))
+            if not two_norms:
+                lw["LS_MIX"] = dev(t(p + "ls1"))
+        if two_norms and ls.mlp:
+            lw["NORM2"] = dev(t(p + "norm2"))
         if ls.mixer == "rglru":
             lw["RGLRU_IN"] = dev(torch.cat([t(mx + "y"), t(mx + "x")]))
             lw["RGLRU_IN_B"] = dev(torch.cat([t(mx + "y.b"), t(mx + "x.b")]))
@@ -276,21 +325,38 @@ def pack_hybrid_weights(spec: HybridSpec, raw: dict[str, torch.Tensor], dtype: t
             lw["MLSTM_IN"] = dev(torch.cat([t(mx + s) for s in ("q", "k", "v", "g", "i", "f")]))
             lw["MLSTM_IB"], lw["MLSTM_FB"], lw["MIX_NORM"] = dev(t(mx + "i.b")), dev(t(mx + "f.b")), dev(t(mx + "norm"))
         else:
-            lw["LAT_DOWN"] = dev(torch.cat([t(mx + "dq"), t(mx + "dkv")]))
-            lw["LAT_QNORM"], lw["LAT_KVNORM"] = dev(t(mx + "dq.norm")), dev(t(mx + "dkv.norm"))
-            lw["LAT_UQ"], lw["LAT_UV"], lw["LAT_SINK"] = dev(t(mx + "uq")), dev(t(mx + "uv")), dev(t(mx + "sink"))
+            if ls.q_rank > 0:
+                lw["LAT_DOWN"] = dev(torch.cat([t(mx + "dq"), t(mx + "dkv")]))
+                lw["LAT_QNORM"], lw["LAT_UQ"] = dev(t(mx + "dq.norm")), dev(t(mx + "uq"))
+            else:   # full-rank queries: everything that reads the mixer's input is one matrix
+                rows = [t(mx + "q")] + ([t(mx + "dkv")] if ls.kv_from < 0 else []) + ([t(mx + "g")] if ls.out_gate else [])
+                lw["LAT_IN"] = dev(torch.cat(rows))
+            if ls.kv_from < 0:
+                lw["LAT_KVNORM"] = dev(t(mx + "dkv.norm"))
+            if ls.learned_sink:
+                lw["LAT_SINK"] = dev(t(mx + "sink"))
+            lw["LAT_UV"] = dev(t(mx + "uv"))
             lw["LAT_UKT"] = dev(t(mx + "uk").view(ls.heads, ls.dim, ls.kv_rank).transpose(1, 2))
+        if ls.mlp == "ffn":
+            q = p + "mlp."
+            lw["FFN_IN"], lw["FFN_IN_B"] = dev(t(q + "up")), dev(t(q + "up.b"))
+            lw["FFN_OUT"], lw["FFN_OUT_B"] = dev(t(q + "down")), dev(t(q + "down.b"))
         if ls.mlp == "dense":
             q = p + "mlp."
             lw["NORM2"] = dev(t(p + "norm2"))
             lw["GLU_IN"], lw["GLU_OUT"] = dev(torch.cat([t(q + "gate"), t(q + "up")])), dev(t(q + "down"))
         if ls.mlp == "moe":
             q = p + "mlp."
-            lw["LS_MLP"], lw["ROUTER"] = dev(t(p + "ls2")), dev(t(q + "router"))
+            lw["ROUTER"] = dev(t(q + "router"))
+            if not two_norms:
+                lw["LS_MLP"] = dev(t(p + "ls2"))
+            if ls.route_bias:
+                lw["ROUTER_BIAS"] = dev(t(q + "correction"))
             lw["EXPERT_IN"] = dev(torch.stack([torch.cat([t(f"{q}e{e}.gate"), t(f"{q}e{e}.up")]) for e in range(ls.experts)]))
             lw["EXPERT_OUT"] = dev(torch.stack([t(f"{q}e{e}.down") for e in range(ls.experts)]))
             if ls.shared_ff:
-                lw["SHARED_IN"] = dev(torch.cat([t(q + "shared.gate"), t(q + "shared.up"), t(q + "shared.sg").reshape(1, -1)]))
+                lw["SHARED_IN"] = dev(torch.cat([t(q + "shared.gate"), t(q + "shared.up")] +
+                                                ([t(q + "shared.sg").reshape(1, -1)] if ls.shared_gate else [])))
                 lw["SHARED_OUT"] = dev(t(q + "shared.down"))
         w["layers"].append(lw)
     return w

@@ -54,6 +54,9 @@ class HybLayerCfg(C.Structure):
         ("decay_mult", C.c_float),
         ("d_heads", C.c_int32), ("d_kv_heads", C.c_int32), ("d_dim", C.c_int32), ("d_vdim", C.c_int32),
         ("left_scale", C.c_float), ("right_scale", C.c_float),
+        ("rot_interleaved", C.c_int32), ("kv_from", C.c_int32), ("out_gate", C.c_int32), ("learned_sink", C.c_int32),
+        ("identity", C.c_int32), ("route_softmax", C.c_int32), ("route_bias", C.c_int32), ("group_best", C.c_int32),
+        ("route_renorm", C.c_int32), ("expert_act", C.c_int32), ("shared_gate", C.c_int32), ("ff_act", C.c_int32),
     ]
 
 
@@ -71,12 +74,14 @@ class HybCfg(C.Structure):
 # hybrid-model enums (include/ssdk.h)
 DT_F32, DT_BF16 = 0, 1
 MIX_WKV, MIX_MLSTM, MIX_LATENT_ATTN, MIX_RGLRU, MIX_SELECTIVE, MIX_ATTN_DELTA = 0, 1, 2, 3, 4, 5
-MLP_NONE, MLP_MOE, MLP_GLU = 0, 1, 2
-BLOCK_PARALLEL_PRENORM, BLOCK_SERIAL_POSTNORM = 0, 1
+MLP_NONE, MLP_MOE, MLP_GLU, MLP_FFN = 0, 1, 2, 3
+ACT_CLAMPED, ACT_SILU, ACT_GELU_TANH, ACT_RELU2 = 0, 1, 2, 3
+BLOCK_PARALLEL_PRENORM, BLOCK_SERIAL_POSTNORM, BLOCK_PARALLEL_TWO_NORMS = 0, 1, 2
 HT_NAMES = ("EMBED HEAD FINAL_NORM NORM LS_MIX LS_MLP WKV_MU WKV_R WKV_K WKV_V WKV_G WKV_W1 WKV_W2 WKV_W0 WKV_U MLSTM_IN "
             "MLSTM_IB MLSTM_FB LAT_DOWN LAT_QNORM LAT_KVNORM LAT_UQ LAT_UKT LAT_UV LAT_SINK MIX_NORM MIX_OUT ROUTER "
             "EXPERT_IN EXPERT_OUT SHARED_IN SHARED_OUT NORM2 GLU_IN GLU_OUT CONV_W CONV_B RGLRU_IN RGLRU_IN_B RGLRU_GATE "
-            "RGLRU_GATE_B RGLRU_LAM SEL_IN SEL_X SEL_DT SEL_DT_B SEL_ALOG SEL_D PAIR_IN ATTN_OUT DELTA_ALOG DELTA_DT_B").split()
+            "RGLRU_GATE_B RGLRU_LAM SEL_IN SEL_X SEL_DT SEL_DT_B SEL_ALOG SEL_D PAIR_IN ATTN_OUT DELTA_ALOG DELTA_DT_B "
+            "LAT_IN FFN_IN FFN_IN_B FFN_OUT FFN_OUT_B ROUTER_BIAS").split()
 HT = {n: i for i, n in enumerate(HT_NAMES)}
 
 # weight kinds (enum in include/ssdk.h)
