@@ -54,6 +54,7 @@ struct ssdk_hyb_engine {
   // tcgen05 path of the dense bf16 products: TMA descriptors by (pointer, rows, K, box rows), split-K partials
   bool use_tc = true;
   bool use_decode_attn = true;  // fused single-token latent attention (SSDK_HYB_DECODE_ATTN=0: GEMM path for every row)
+  bool use_decode_mma = true;   // its tensor-core form for bf16 storage (SSDK_HYB_DECODE_MMA=0: the CUDA-core form)
   std::map<std::tuple<const void*, int64_t, int, int>, CUtensorMap> tmaps;
   float* partials = nullptr; size_t partial_floats = 0;
   int tmap(const void* ptr, int64_t rows, int K, int box_rows, const CUtensorMap** out) {
@@ -486,7 +487,19 @@ struct HybRun {
           ssdk::LatentDecodeArgs da;
           da.qcat = e->qcat; da.cache = pool; da.sink = sink; da.part = e->att_s; da.out = e->t0;
           da.H = H; da.KR = KR; da.W = Wd; da.splits = splits; da.scale = c.attn_scale; da.pool_aligned = ((uintptr_t)pool & 15) == 0;
-          CKI(L.go(ssdk::latent_decode_partial_kernel<T>, dim3(rg.n_seqs, splits), dim3(ssdk::kDecThreads), smem, da, rg));
+          // bf16 rows that start on 16-byte boundaries go through the tensor cores: k-steps of 16 columns and n-tiles of 8
+          // latent columns per warp pick the instantiation
+          const int ks_per = ((Wd + 15) / 16 + 3) / 4, nt_per = ((KR + 7) / 8 + 3) / 4;
+          const bool mma = !kF32 && e->use_decode_mma && da.pool_aligned && Wd % 8 == 0 && KR % 8 == 0 && ks_per <= 9 && nt_per <= 16;
+          if (mma) {
+            const dim3 grid(rg.n_seqs, splits, (H + 15) / 16), block(ssdk::kDmThreads);
+            const size_t sm = ssdk::latent_decode_mma_smem(Wd);
+            if (ks_per <= 3 && nt_per <= 4) CKI(L.go(ssdk::latent_decode_mma_kernel<3, 4>, grid, block, sm, da, rg));
+            else if (ks_per <= 5 && nt_per <= 8) CKI(L.go(ssdk::latent_decode_mma_kernel<5, 8>, grid, block, sm, da, rg));
+            else CKI(L.go(ssdk::latent_decode_mma_kernel<9, 16>, grid, block, sm, da, rg));
+          } else {
+            CKI(L.go(ssdk::latent_decode_partial_kernel<T>, dim3(rg.n_seqs, splits), dim3(ssdk::kDecThreads), smem, da, rg));
+          }
           CKI(L.go(ssdk::latent_decode_merge_kernel<T>, dim3(rg.n_seqs, H), dim3(128), 0, da, rg));
           fused_decode = true;
         }
@@ -857,6 +870,9 @@ static int hyb_smem_attrs(ssdk_hyb_engine* e) {
 #undef SSDK_SCAN_ATTR
   CK(cudaFuncSetAttribute(ssdk::latent_decode_partial_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   CK(cudaFuncSetAttribute(ssdk::latent_decode_partial_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  CK(cudaFuncSetAttribute(ssdk::latent_decode_mma_kernel<3, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  CK(cudaFuncSetAttribute(ssdk::latent_decode_mma_kernel<5, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  CK(cudaFuncSetAttribute(ssdk::latent_decode_mma_kernel<9, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   CK(cudaFuncSetAttribute(ssdk::delta_scan_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   CK(cudaFuncSetAttribute(ssdk::delta_scan_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   CK(cudaFuncSetAttribute(ssdk::delta_scan_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
@@ -944,6 +960,7 @@ int ssdk_hyb_create(const ssdk_hyb_cfg* cfg, const ssdk_hyb_layer_cfg* layers, s
   e->esz = cfg->dtype == SSDK_DT_BF16 ? 2 : 4;
   e->use_tc = env_int("SSDK_HYB_TCGEN05", 1) != 0;
   e->use_decode_attn = env_int("SSDK_HYB_DECODE_ATTN", 1) != 0;
+  e->use_decode_mma = env_int("SSDK_HYB_DECODE_MMA", 1) != 0;
   e->layers.resize(cfg->n_layers);
   for (int i = 0; i < cfg->n_layers; ++i) e->layers[i].c = layers[i];
   if (hyb_derive(e) != 0) { delete e; return -1; }

@@ -282,6 +282,169 @@ __global__ void __launch_bounds__(kDecThreads) latent_decode_partial_kernel(cons
   for (int h = tid; h < H; h += kDecThreads) { dst[(size_t)h * (KR + 2) + KR] = mx[h]; dst[(size_t)h * (KR + 2) + KR + 1] = ls[h]; }
 }
 
+// ---- the same split-context pass on the tensor cores (bf16 storage, rows of the pool 16-byte aligned) ----
+// grid (n_seqs, splits, head groups of 16), four warps.  The queries of up to 16 heads are the 16 rows of an m16n8k16
+// tile: a warp keeps the A fragments of ITS quarter of the W = kv_rank + rot_dim columns in registers for the whole
+// pass, so a tile of 32 keys (cp.async, double buffered, rows beyond the split zero-filled) is read from shared memory
+// once for the scores — the four warps' partial products are summed through shared memory — and once more, transposed
+// by ldmatrix, as the B operand of P C, where every warp owns a quarter of the latent columns (NT n-tiles of 8).
+// Scores, maximum, sum and the rescaling stay fp32; P is rounded to bf16 for the product like on the GEMM path.
+// Writes the same partials as latent_decode_partial_kernel, so latent_decode_merge_kernel joins them.
+constexpr int kDmKeys = 32, kDmThreads = 128;
+
+inline int latent_decode_mma_ldk(int W) { return (W + 15) / 16 * 16 + 8; }   // padded row (elements) of queries and keys in shared memory
+inline size_t latent_decode_mma_smem(int W) {
+  return (size_t)(2 * kDmKeys + 16) * latent_decode_mma_ldk(W) * 2 + (size_t)4 * 16 * (kDmKeys + 1) * 4 + (size_t)16 * (kDmKeys + 8) * 2 + 3 * 16 * 4;
+}
+
+template <int KS, int NT>
+__global__ void __launch_bounds__(kDmThreads) latent_decode_mma_kernel(const LatentDecodeArgs p, const Ragged rg) {
+  const int s = blockIdx.x, j = blockIdx.y, h0 = blockIdx.z * 16;
+  const int row = rg.cu[s];
+  if (rg.cu[s + 1] - row != 1) return;
+  const int H = p.H, KR = p.KR, W = p.W, LDK = (W + 15) / 16 * 16 + 8, nh = min(16, H - h0);
+  extern __shared__ __align__(16) uint8_t dm_smem[];
+  __nv_bfloat16* kt = (__nv_bfloat16*)dm_smem;                 // [2][kDmKeys][LDK] key tiles
+  __nv_bfloat16* qs = kt + (size_t)2 * kDmKeys * LDK;          // [16][LDK] queries (rows beyond the heads are zero)
+  float* sp = (float*)(qs + (size_t)16 * LDK);                 // [4][16][kDmKeys + 1] partial scores per warp
+  __nv_bfloat16* pb = (__nv_bfloat16*)(sp + 4 * 16 * (kDmKeys + 1));   // [16][kDmKeys + 8] weights
+  float* mx = (float*)(pb + 16 * (kDmKeys + 8));               // [16] running maximum
+  float* ls = mx + 16;                                         // [16] running sum
+  float* rs = ls + 16;                                         // [16] rescale of this tile
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
+  const int ctx = rg.pos0[s] + 1, per = (ctx + p.splits - 1) / p.splits;
+  const int k_lo = j * per, k_hi = min(ctx, k_lo + per);
+  const int vpr = W / 8;   // 16-byte vectors per row
+  const __nv_bfloat16* cache = (const __nv_bfloat16*)p.cache;
+  auto load_tile = [&](int k0, int buf) {
+    __nv_bfloat16* dst = kt + (size_t)buf * kDmKeys * LDK;
+    for (int i = tid; i < kDmKeys * vpr; i += kDmThreads) {
+      const int k = i / vpr, v = i - k * vpr;
+      const bool ok = k0 + k < k_hi;
+      const __nv_bfloat16* src = ok ? cache + page_row(rg, s, k0 + k) * (size_t)W + v * 8 : cache;
+      cp_async16(dst + (size_t)k * LDK + v * 8, src, ok);
+    }
+    cp_async_commit();
+  };
+  if (k_lo < k_hi) load_tile(k_lo, 0);
+  // queries, padding columns of all three buffers, running statistics
+  const __nv_bfloat16* q = (const __nv_bfloat16*)p.qcat + ((size_t)row * H + h0) * W;
+  for (int i = tid; i < 16 * LDK; i += kDmThreads) {
+    const int r = i / LDK, c = i - r * LDK;
+    qs[i] = (r < nh && c < W) ? q[(size_t)r * W + c] : __float2bfloat16_rn(0.f);
+  }
+  for (int i = tid; i < 2 * kDmKeys * (LDK - W); i += kDmThreads) {
+    const int r = i / (LDK - W), c = W + i % (LDK - W);
+    kt[(size_t)r * LDK + c] = __float2bfloat16_rn(0.f);
+  }
+  if (tid < 16) { mx[tid] = -INFINITY; ls[tid] = 0.f; }
+  __syncthreads();
+  const int nks = (W + 15) / 16, ks_per = (nks + 3) / 4, ks0 = warp * ks_per, my_ks = max(0, min(ks_per, nks - ks0));
+  uint32_t qa[KS][4];
+#pragma unroll
+  for (int i = 0; i < KS; ++i)
+    if (i < my_ks) ldmatrix_x4(qa[i], qs + (size_t)(lane & 15) * LDK + (ks0 + i) * 16 + (lane >> 4) * 8);
+  float acc[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  const int ntiles = (KR + 7) / 8, nt0 = warp * NT;   // this warp's latent columns: n-tiles nt0 .. nt0 + NT - 1
+  int buf = 0;
+  for (int k0 = k_lo; k0 < k_hi; k0 += kDmKeys, buf ^= 1) {
+    cp_async_wait<0>();
+    __syncthreads();   // the tile has landed; everyone is done with the other buffer
+    if (k0 + kDmKeys < k_hi) load_tile(k0 + kDmKeys, buf ^ 1);
+    const __nv_bfloat16* tile = kt + (size_t)buf * kDmKeys * LDK;
+    float sc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+#pragma unroll
+    for (int i = 0; i < KS; ++i)
+      if (i < my_ks) {
+        const int kk = (ks0 + i) * 16;
+#pragma unroll
+        for (int nj = 0; nj < 2; ++nj) {
+          uint32_t b[4];
+          ldmatrix_x4(b, tile + (size_t)(nj * 16 + (lane >> 4) * 8 + (lane & 7)) * LDK + kk + ((lane >> 3) & 1) * 8);
+          mma_bf16_16816(sc[2 * nj], qa[i], b[0], b[1]);
+          mma_bf16_16816(sc[2 * nj + 1], qa[i], b[2], b[3]);
+        }
+      }
+    float* spw = sp + warp * 16 * (kDmKeys + 1);
+#pragma unroll
+    for (int ni = 0; ni < 4; ++ni) {
+      spw[g * (kDmKeys + 1) + ni * 8 + 2 * t4] = sc[ni][0];
+      spw[g * (kDmKeys + 1) + ni * 8 + 2 * t4 + 1] = sc[ni][1];
+      spw[(g + 8) * (kDmKeys + 1) + ni * 8 + 2 * t4] = sc[ni][2];
+      spw[(g + 8) * (kDmKeys + 1) + ni * 8 + 2 * t4 + 1] = sc[ni][3];
+    }
+    __syncthreads();
+    {
+      // row r of the tile: eight threads, four keys each (fp32 softmax step)
+      const int r = tid >> 3, sub = tid & 7, nk = min(kDmKeys, k_hi - k0);
+      float v[4], m_new = mx[r];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int k = sub * 4 + c;
+        float a = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) a += sp[(w * 16 + r) * (kDmKeys + 1) + k];
+        v[c] = k < nk ? a * p.scale : -INFINITY;
+        m_new = fmaxf(m_new, v[c]);
+      }
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, o));
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float w = v[c] == -INFINITY ? 0.f : expf(v[c] - m_new);
+        pb[r * (kDmKeys + 8) + sub * 4 + c] = __float2bfloat16_rn(w);
+        sum += w;
+      }
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      const float m_old = mx[r];
+      const float resc = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+      __syncwarp();
+      if (sub == 0) { mx[r] = m_new; ls[r] = ls[r] * resc + sum; rs[r] = resc; }
+    }
+    __syncthreads();
+    const float r_lo = rs[g], r_hi = rs[g + 8];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) { acc[i][0] *= r_lo; acc[i][1] *= r_lo; acc[i][2] *= r_hi; acc[i][3] *= r_hi; }
+#pragma unroll
+    for (int kk = 0; kk < kDmKeys; kk += 16) {
+      uint32_t pa[4];
+      ldmatrix_x4(pa, pb + (size_t)(lane & 15) * (kDmKeys + 8) + kk + (lane >> 4) * 8);
+#pragma unroll
+      for (int i = 0; i < NT; i += 2) {
+        if (nt0 + i >= ntiles) continue;
+        uint32_t vb[4];
+        const int mi = lane >> 3, rr = lane & 7;
+        // (a second n-tile beyond the latent columns reads the rotated part or the zero padding: its result is dropped)
+        ldmatrix_x4_trans(vb, tile + (size_t)(kk + (mi & 1) * 8 + rr) * LDK + (nt0 + i) * 8 + (mi >> 1) * 8);
+        mma_bf16_16816(acc[i], pa, vb[0], vb[1]);
+        if (i + 1 < NT) mma_bf16_16816(acc[i + 1], pa, vb[2], vb[3]);
+      }
+    }
+  }
+  __syncthreads();
+  float* dst = p.part + (((size_t)s * p.splits + j) * H + h0) * (KR + 2);
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+    const int c = (nt0 + i) * 8 + 2 * t4;
+    if (nt0 + i >= ntiles) continue;
+    if (g < nh) {
+      if (c < KR) dst[(size_t)g * (KR + 2) + c] = acc[i][0];
+      if (c + 1 < KR) dst[(size_t)g * (KR + 2) + c + 1] = acc[i][1];
+    }
+    if (g + 8 < nh) {
+      if (c < KR) dst[(size_t)(g + 8) * (KR + 2) + c] = acc[i][2];
+      if (c + 1 < KR) dst[(size_t)(g + 8) * (KR + 2) + c + 1] = acc[i][3];
+    }
+  }
+  if (tid < nh) { dst[(size_t)tid * (KR + 2) + KR] = mx[tid]; dst[(size_t)tid * (KR + 2) + KR + 1] = ls[tid]; }
+}
+
 // grid (n_seqs, H): out = sum_j e^(m_j - m) acc_j / (e^(sink - m) + sum_j e^(m_j - m) l_j), m = max(sink, max_j m_j)
 template <typename T>
 __global__ void latent_decode_merge_kernel(const LatentDecodeArgs p, const Ragged rg) {

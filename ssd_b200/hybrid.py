@@ -385,8 +385,38 @@ def random_hybrid_weights(spec: HybridSpec, dtype: torch.dtype, device, seed: in
 
     if spec.block == L.BLOCK_SERIAL_POSTNORM:
         w["FINAL_NORM"] = vec(W, 1.0)
+    if spec.block == L.BLOCK_PARALLEL_TWO_NORMS:
+        w["FINAL_NORM"] = vec(W, 1.0)
+        if spec.tied_head:   # the table is read as it is by the head: unit-size logits, the embedding's scale restores O(1) rows
+            w["EMBED"] = (torch.randn(spec.vocab, W, generator=g, device=device) / W ** 0.5).to(dtype)
+            w["HEAD"] = w["EMBED"]
     for ls in spec.layers:
         H, D, V = ls.heads, ls.dim, ls.vdim
+        if spec.block == L.BLOCK_PARALLEL_TWO_NORMS:
+            if ls.mixer != "latent_attention" or ls.q_rank:
+                raise ValueError("random weights of two-norm blocks are made for latent attention with full-rank queries")
+            R, KR, own = ls.rot_dim, ls.kv_rank, ls.kv_from < 0
+            lw = {"NORM": vec(W, 1.0), "MIX_OUT": lin(W, H * V), "LAT_UV": lin(H * V, KR),
+                  "LAT_IN": lin(H * (D + R) + (KR + R if own else 0) + (H * V if ls.out_gate else 0), W),
+                  "LAT_UKT": (lin(H, KR, D) * (D / KR) ** 0.5).contiguous()}
+            if own:
+                lw["LAT_KVNORM"] = vec(KR, 1.0)
+            if ls.learned_sink:
+                lw["LAT_SINK"] = vec(H, 0.0, 1.0)
+            if ls.mlp:
+                lw["NORM2"] = vec(W, 1.0)
+            if ls.mlp == "ffn":
+                lw["FFN_IN"], lw["FFN_IN_B"], lw["FFN_OUT"], lw["FFN_OUT_B"] = lin(ls.ff, W), vec(ls.ff), lin(W, ls.ff), vec(W)
+            elif ls.mlp == "moe":
+                lw["ROUTER"] = lin(ls.experts + ls.identity, W)
+                if ls.route_bias:
+                    lw["ROUTER_BIAS"] = vec(ls.experts + ls.identity, 0.0, 0.02)
+                lw["EXPERT_IN"], lw["EXPERT_OUT"] = lin(ls.experts, 2 * ls.ff, W), lin(ls.experts, W, ls.ff)
+                if ls.shared_ff:
+                    lw["SHARED_IN"] = lin(2 * ls.shared_ff + (1 if ls.shared_gate else 0), W)
+                    lw["SHARED_OUT"] = lin(W, ls.shared_ff)
+            w["layers"].append(lw)
+            continue
         if ls.mixer in ("rglru", "mamba1", "parallel"):
             lw = {"NORM": vec(W, 1.0)}
             taps = ls.conv

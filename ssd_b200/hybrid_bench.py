@@ -1,8 +1,11 @@
-"""Throughput of the hybrid families (bench.py --arch pikavik | kefurax).
+"""Throughput of the hybrid families (bench.py --arch pikavik | kefurax | lisenex).
 
 --arch pikavik: a Pikavik stack beside the closest dense model of the framework (below).
 --arch kefurax: a Kefurax stack (attention + delta-rule pair with a dense feed-forward, selective scan, rglru, ...) beside
 the closest existing model of the framework, a Pikavik stack of the same width, depth and active feed-forward size.
+--arch lisenex: a Lisenex stack (latent attention with full-rank queries in every layer, every second layer reading the
+layer before's latent pool; a dense squared-relu feed-forward first, then softmax-routed experts with identity experts and a
+shared expert) beside the same Pikavik stack.
 
 For every size: a Pikavik stack (mLSTM, wkv, wkv, latent attention, ... each with a grouped mixture of experts and a
 shared expert) with random weights, and a Llama stack of the same width, depth and ACTIVE feed-forward size
@@ -62,6 +65,29 @@ def kefurax_spec(z):
     return HybridSpec(W, z["vocab"], 1e-6, layers, architecture="Kefurax", embed_scale=1.0, residual_mult=0.7)
 
 
+def lisenex_spec(z):
+    """Layers that resemble a real model's: 16 heads of 64 / 128 unrotated + 64 rotated query dimensions over a latent of
+    256 / 512, values as wide as the keys; layer 2k+1 reads layer 2k's latent pool; the first feed-forward is dense (as wide
+    as a token's active experts), the others route over `experts` outputs, two of them identity experts."""
+    from . import lib as L
+    from .hybrid import DESIGNS, HybridSpec, LayerSpec
+    d = DESIGNS["Lisenex"]
+    layers = []
+    for i in range(z["layers"]):
+        ls = LayerSpec("latent_attention", z["lh"], z["ld"], z["ld"], rot_dim=z["rot"], rot_dims=z["rot"], rot_base=10000.0,
+                       kv_rank=z["kvr"], q_rank=0, attn_scale=(z["ld"] + z["rot"]) ** -0.5, kv_from=(i - 1 if i % 2 else -1),
+                       **d["latent"])
+        if i == 0:
+            ls.mlp, ls.ff, ls.ff_act = "ffn", z["top"] * z["ff"] + z["sff"], d["ffn"]["ff_act"]
+        else:
+            ls.mlp, ls.experts, ls.identity, ls.top, ls.groups, ls.keep = "moe", z["experts"] - 2, 2, z["top"], z["groups"], z["keep"]
+            ls.ff, ls.shared_ff = z["ff"], z["sff"]
+            for k, v in d["moe"].items():
+                setattr(ls, k, v)
+        layers.append(ls)
+    return HybridSpec(z["width"], z["vocab"], 1e-6, layers, architecture="Lisenex", embed_scale=float(z["width"]) ** 0.5)
+
+
 def _events(fn, warmup, steps):
     for _ in range(warmup):
         fn()
@@ -99,7 +125,8 @@ def run_pikavik(z, prompt, batch, warmup, steps, dtype="bfloat16", spec_fn=pikav
                                     temps=[0.0] * batch), warmup, steps)
     launches_decode = (r.launch_count - n0) // (warmup + steps)
     params = sum(t.numel() for lw in w["layers"] for t in lw.values()) + w["HEAD"].numel()
-    active = params - sum(lw["EXPERT_IN"].numel() + lw["EXPERT_OUT"].numel() for lw in w["layers"] if "EXPERT_IN" in lw) * (1 - z["top"] / z["experts"])
+    active = params - sum((lw["EXPERT_IN"].numel() + lw["EXPERT_OUT"].numel()) * (1 - min(1.0, ls.top / ls.experts))
+                          for lw, ls in zip(w["layers"], spec.layers) if "EXPERT_IN" in lw)
     r.close()
     return {"prefill_ms": pre, "prefill_tok_s": prompt / pre * 1e3, "decode_ms": dec, "decode_tok_s": batch / dec * 1e3,
             "launches_prefill": launches_prefill, "launches_decode": launches_decode, "params": int(params),
@@ -167,9 +194,30 @@ def run_kefurax(args):
     return out
 
 
+def run_lisenex(args):
+    out = {"metric": "prefill and decode tokens/s, Lisenex beside Pikavik at equal width / depth / active feed-forward",
+           "dtype": "bf16", "data": "synthetic (random weights, random token ids)", "n_gpus": 1, "steps": args.steps,
+           "warmup": args.warmup, "timing": "CUDA events around the public forward call, median; every pass streams the stack's "
+           "weights (> 126 MB L2 for size m; size s partly L2-resident, stated here)", "sizes": {}}
+    names = [args.hybrid_size] if args.hybrid_size != "all" else list(SIZES)
+    for name in names:
+        z = SIZES[name]
+        row = {"config": {k: z[k] for k in ("width", "layers", "experts", "top", "ff", "sff", "vocab")}, "prompt": args.prompt_len_hybrid,
+               "decode_batch": args.hybrid_batch}
+        row["lisenex"] = run_pikavik(z, args.prompt_len_hybrid, args.hybrid_batch, args.warmup, args.steps, spec_fn=lisenex_spec)
+        if not args.no_dense_arm:
+            row["pikavik"] = run_pikavik(z, args.prompt_len_hybrid, args.hybrid_batch, args.warmup, args.steps)
+        if args.hybrid_fp32:
+            row["lisenex_fp32"] = run_pikavik(z, args.prompt_len_hybrid, args.hybrid_batch, args.warmup, args.steps, "float32", lisenex_spec)
+        out["sizes"][name] = row
+    return out
+
+
 def run(args):
     if getattr(args, "arch", "pikavik") == "kefurax":
         return run_kefurax(args)
+    if getattr(args, "arch", "pikavik") == "lisenex":
+        return run_lisenex(args)
     out = {"metric": "prefill and decode tokens/s, Pikavik beside Llama at equal width / depth / active feed-forward",
            "dtype": "bf16", "data": "synthetic (random weights, random token ids)", "n_gpus": 1, "steps": args.steps,
            "warmup": args.warmup, "timing": "CUDA events around the public forward call, median; every pass streams the stack's "

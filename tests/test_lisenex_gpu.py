@@ -280,6 +280,40 @@ def test_bfloat16_storage(tmp_path, width):
     assert U.rel_err(np.concatenate(out), whole) < 1e-2
 
 
+def test_bfloat16_decode_attention_on_tensor_cores(tmp_path, monkeypatch):
+    """Single-token rows of bf16 models whose cached rows start on 16-byte boundaries take the tensor-core form of the
+    split-context attention: more than 16 heads (two head groups), latent sizes that end inside an n-tile pair, a column
+    count that is no multiple of 16 (zero padding), three instantiations, contexts from a few keys (empty splits, a partly
+    filled tile) to hundreds.  Against the oracle, and against the CUDA-core form of the same pass."""
+    cfg = U.config([U.latent(heads=20, dim=16, rot_dim=16, vdim=8, kv_rank=40, scale=1.5, mlp=U.dense(ff=64)),
+                    U.latent(kv_from=0, heads=3, dim=8, rot_dim=16, vdim=24, kv_rank=40, scale=1.0),
+                    U.latent(heads=6, dim=16, rot_dim=64, vdim=16, kv_rank=128, scale=0.5),
+                    U.latent(heads=2, dim=24, rot_dim=8, vdim=16, kv_rank=136, scale=0.5)], width=64)
+    tensors = U.random_tensors(cfg, 9)
+    path = U.write_checkpoint(str(tmp_path / "dec"), cfg, tensors)
+    plain = PlainModel(cfg, tensors)
+    lens, steps = [5, 70, 333], 5
+    seqs = [_tokens(n + steps, cfg["vocab"], 100 + i) for i, n in enumerate(lens)]
+    refs = [plain.run(s).numpy() for s in seqs]
+    pages = [_pages(len(s), 16, first) for s, first in zip(seqs, (0, 3, 10))]
+    got = {}
+    for mma in ("1", "0"):
+        monkeypatch.setenv("SSDK_HYB_DECODE_MMA", mma)
+        r = _load(path, "bfloat16", num_blocks=40)
+        for i in range(3):
+            r.forward([(seqs[i][:lens[i]], 0, i, pages[i], [lens[i] - 1])])
+        out = [[] for _ in seqs]
+        for t in range(steps):
+            lg, _ = r.forward([([seqs[i][lens[i] + t]], lens[i] + t, i, pages[i], [0]) for i in range(3)])
+            for i in range(3):
+                out[i].append(lg[i:i + 1])
+        got[mma] = [np.concatenate(o) for o in out]
+        r.close()
+    for i in range(3):
+        assert U.rel_err(got["1"][i], refs[i][lens[i]:]) < BF16_TOL, f"sequence {i}"
+        assert U.rel_err(got["1"][i], got["0"][i]) < 1e-2, f"sequence {i}: the two forms of the pass disagree"
+
+
 def test_bfloat16_calls_of_many_rows(tmp_path):
     """More rows than one tile of the tcgen05 GEMM holds (256): the dense projections run as row chunks of one launch, the
     last chunk partly filled; two prompts of unequal length in one call, against the oracle and against portions."""
