@@ -500,7 +500,7 @@ struct HybRun {
           } else {
             CKI(L.go(ssdk::latent_decode_partial_kernel<T>, dim3(rg.n_seqs, splits), dim3(ssdk::kDecThreads), smem, da, rg));
           }
-          CKI(L.go(ssdk::latent_decode_merge_kernel<T>, dim3(rg.n_seqs, H), dim3(128), 0, da, rg));
+          CKI(L.go(ssdk::latent_decode_merge_kernel<T>, dim3(rg.n_seqs, H, (KR + 127) / 128), dim3(128), 0, da, rg));
           fused_decode = true;
         }
       }

@@ -445,33 +445,42 @@ __global__ void __launch_bounds__(kDmThreads) latent_decode_mma_kernel(const Lat
   if (tid < nh) { dst[(size_t)tid * (KR + 2) + KR] = mx[tid]; dst[(size_t)tid * (KR + 2) + KR + 1] = ls[tid]; }
 }
 
-// grid (n_seqs, H): out = sum_j e^(m_j - m) acc_j / (e^(sink - m) + sum_j e^(m_j - m) l_j), m = max(sink, max_j m_j)
+// grid (n_seqs, H, column chunks of the block size): out = sum_j e^(m_j - m) acc_j / (e^(sink - m) + sum_j e^(m_j - m) l_j), m = max(sink, max_j m_j)
+constexpr int kDecMaxSplits = 32;   // the host never asks for more context splits
+
 template <typename T>
 __global__ void latent_decode_merge_kernel(const LatentDecodeArgs p, const Ragged rg) {
+  __shared__ float wj[kDecMaxSplits];   // e^(m_j - m) / denominator per split (0 for a split without keys)
   const int s = blockIdx.x, h = blockIdx.y;
   const int row = rg.cu[s];
   if (rg.cu[s + 1] - row != 1) return;
   const int KR = p.KR;
   const float* part = p.part + ((size_t)s * p.splits * p.H + h) * (KR + 2);
   const size_t js = (size_t)p.H * (KR + 2);  // floats between two splits of one head
-  const float sk = p.sink ? ld_f<T>((const T*)p.sink + h) : -INFINITY;
-  float m = sk;
-  for (int j = 0; j < p.splits; ++j) m = fmaxf(m, part[j * js + KR]);
-  float den = expf(sk - m);
-  for (int j = 0; j < p.splits; ++j) {
-    const float mj = part[j * js + KR];
-    if (mj != -INFINITY) den += expf(mj - m) * part[j * js + KR + 1];
+  if (threadIdx.x < 32) {
+    const int j = threadIdx.x;
+    const float sk = p.sink ? ld_f<T>((const T*)p.sink + h) : -INFINITY;
+    const float mj = j < p.splits ? part[j * js + KR] : -INFINITY;
+    const float m = fmaxf(sk, warp_max(mj));
+    const float w = mj == -INFINITY ? 0.f : expf(mj - m);
+    const float den = warp_sum(j < p.splits ? w * part[j * js + KR + 1] : 0.f) + (sk == -INFINITY ? 0.f : expf(sk - m));
+    if (j < p.splits) wj[j] = w / den;
   }
-  const float inv = 1.0f / den;
+  __syncthreads();
   T* out = (T*)p.out + ((size_t)row * p.H + h) * KR;
-  for (int c = threadIdx.x; c < KR; c += blockDim.x) {
-    float a = 0.f;
-    for (int j = 0; j < p.splits; ++j) {
-      const float mj = part[j * js + KR];
-      if (mj != -INFINITY) a = fmaf(expf(mj - m), part[j * js + c], a);
-    }
-    st_f<T>(out + c, a * inv);
+  // a thread per latent column (blockIdx.z picks the chunk of columns), four independent sums so that the loads overlap
+  const int c = blockIdx.z * blockDim.x + threadIdx.x;
+  if (c >= KR) return;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  int j = 0;
+  for (; j + 4 <= p.splits; j += 4) {
+    a0 = fmaf(wj[j], part[j * js + c], a0);
+    a1 = fmaf(wj[j + 1], part[(j + 1) * js + c], a1);
+    a2 = fmaf(wj[j + 2], part[(j + 2) * js + c], a2);
+    a3 = fmaf(wj[j + 3], part[(j + 3) * js + c], a3);
   }
+  for (; j < p.splits; ++j) a0 = fmaf(wj[j], part[j * js + c], a0);
+  st_f<T>(out + c, (a0 + a1) + (a2 + a3));
 }
 
 }  // namespace ssdk
