@@ -54,6 +54,7 @@ struct ssdk_hyb_engine {
   // tcgen05 path of the dense bf16 products: TMA descriptors by (pointer, rows, K, box rows), split-K partials
   bool use_tc = true;
   bool use_decode_attn = true;  // fused single-token latent attention (SSDK_HYB_DECODE_ATTN=0: GEMM path for every row)
+  bool use_tc_scores = true;    // score GEMM of latent-attention portions on the tcgen05 GEMM (SSDK_HYB_TC_SCORES=0: mma.sync tile)
   bool use_decode_mma = true;   // its tensor-core form for bf16 storage (SSDK_HYB_DECODE_MMA=0: the CUDA-core form)
   std::map<std::tuple<const void*, int64_t, int, int>, CUtensorMap> tmaps;
   float* partials = nullptr; size_t partial_floats = 0;
@@ -61,6 +62,7 @@ struct ssdk_hyb_engine {
     auto key = std::make_tuple(ptr, rows, K, box_rows);
     auto it = tmaps.find(key);
     if (it == tmaps.end()) {
+      if (tmaps.size() >= 8192) tmaps.clear();   // activations at changing offsets / row counts: keep the table bounded
       CUtensorMap tm;
       CKI(make_tmap(&tm, ptr, rows, K, box_rows));
       it = tmaps.emplace(key, tm).first;
@@ -278,11 +280,13 @@ struct HybRun {
            ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0;
   }
   int lin_tc(const void* A, const void* W, float* C, int m_total, int N, int K) {
-    const CUtensorMap *tmW, *tmX;
-    CKI(e->tmap(W, N, K, 64, &tmW));
+    const CUtensorMap* tm;   // (copied: a later lookup may empty the table)
+    CKI(e->tmap(W, N, K, 64, &tm));
+    const CUtensorMap tmW = *tm;
     // one launch for all rows: chunks of `un` tokens along gridDim.z share the weight tiles through L2
     const int un = umma_n_for(std::min(m_total, kMaxTokens)), chunks = (m_total + un - 1) / un;
-    CKI(e->tmap(A, m_total, K, un, &tmX));
+    CKI(e->tmap(A, m_total, K, un, &tm));
+    const CUtensorMap tmX = *tm;
     const int tiles = (N + kTileRows - 1) / kTileRows, num_kb = K / kBlockK;
     // narrow outputs (a head projection is 8 .. 32 tiles) with few row chunks fill the machine by splitting K
     int S = auto_splits(tiles * chunks, num_kb, un <= 64 ? 2 : 1);
@@ -293,7 +297,7 @@ struct HybRun {
     p.kb_per_split = (num_kb + S - 1) / S;
     S = (num_kb + p.kb_per_split - 1) / p.kb_per_split;
     p.out = S == 1 ? C : e->partials;
-    CKI(launch_gemm(L, un, EPI_PARTIAL, *tmW, *tmX, p, tiles, S, chunks));
+    CKI(launch_gemm(L, un, EPI_PARTIAL, tmW, tmX, p, tiles, S, chunks));
     if (S > 1) {
       const size_t n = (size_t)m_total * N;
       CKI(L.go(ssdk::splitk_sum_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (const float*)e->partials, C, S, n));
@@ -478,19 +482,20 @@ struct HybRun {
       for (int s = 0; s < rg.n_seqs; ++s)
         if (h_cu[s + 1] - h_cu[s] == 1) { ++n_dec; ctx_max = std::max(ctx_max, h_pos0[s] + 1); }
       const size_t smem = ssdk::latent_decode_smem(H, KR, Wd, sizeof(T));
-      if (n_dec > 0 && smem <= 200 * 1024 && e->use_decode_attn) {
+      const bool pool_aligned = ((uintptr_t)pool & 15) == 0;
+      // bf16 rows that start on 16-byte boundaries go through the tensor cores: k-steps of 16 columns and n-tiles of 8
+      // latent columns per warp pick the instantiation; the CUDA-core form holds all heads' queries and sums in shared memory
+      const int ks_per = ((Wd + 15) / 16 + 3) / 4, nt_per = ((KR + 7) / 8 + 3) / 4;
+      const bool mma = !kF32 && e->use_decode_mma && pool_aligned && Wd % 8 == 0 && KR % 8 == 0 && ks_per <= 9 && nt_per <= 16;
+      if (n_dec > 0 && (mma || smem <= 200 * 1024) && e->use_decode_attn) {
         // ~2 CTAs per SM over all sequences, at least 64 keys per split, partials within the score buffer
-        int splits = std::max(1, std::min({32, 2 * num_sms() / n_dec, (ctx_max + 63) / 64}));
+        int splits = std::max(1, std::min({ssdk::kDecMaxSplits, 2 * num_sms() / n_dec, (ctx_max + 63) / 64}));
         const size_t per_split = (size_t)rg.n_seqs * H * (KR + 2);
         splits = (int)std::min<size_t>(splits, e->att_elems / per_split);
         if (splits >= 1) {
           ssdk::LatentDecodeArgs da;
           da.qcat = e->qcat; da.cache = pool; da.sink = sink; da.part = e->att_s; da.out = e->t0;
-          da.H = H; da.KR = KR; da.W = Wd; da.splits = splits; da.scale = c.attn_scale; da.pool_aligned = ((uintptr_t)pool & 15) == 0;
-          // bf16 rows that start on 16-byte boundaries go through the tensor cores: k-steps of 16 columns and n-tiles of 8
-          // latent columns per warp pick the instantiation
-          const int ks_per = ((Wd + 15) / 16 + 3) / 4, nt_per = ((KR + 7) / 8 + 3) / 4;
-          const bool mma = !kF32 && e->use_decode_mma && da.pool_aligned && Wd % 8 == 0 && KR % 8 == 0 && ks_per <= 9 && nt_per <= 16;
+          da.H = H; da.KR = KR; da.W = Wd; da.splits = splits; da.scale = c.attn_scale; da.pool_aligned = pool_aligned;
           if (mma) {
             const dim3 grid(rg.n_seqs, splits, (H + 15) / 16), block(ssdk::kDmThreads);
             const size_t sm = ssdk::latent_decode_mma_smem(Wd);
@@ -514,7 +519,8 @@ struct HybRun {
       for (int q0 = 0; q0 < n; q0 += qb) {
         const int nq = std::min(qb, n - q0), rows = nq * H, cb = (p0 + q0 + nq + 7) / 8 * 8;  // keys this block can see, padded
         const T* qrows = (const T*)e->qcat + (size_t)(r0 + q0) * H * Wd;
-        CKI(lin(qrows, Wd, e->keys, Wd, e->att_s, cb, rows, cb, Wd, false, 1, 0, 0, 0, false));
+        // scores on the tcgen05 GEMM when the row is whole k-blocks (keys are the 128-row operand, (query, head) rows the tokens)
+        CKI(lin(qrows, Wd, e->keys, Wd, e->att_s, cb, rows, cb, Wd, false, 1, 0, 0, 0, e->use_tc_scores));
         CKI(L.go(ssdk::sink_softmax_kernel<T>, dim3(rows), dim3(256), 0, (const float*)e->att_s, (T*)e->att_p,
                  (const T*)sink, H, cb, p0 + q0, c.attn_scale, rows, 0.f));
         CKI(lin(e->att_p, cb, e->lat_t, ctx_pad, (T*)e->t0 + (size_t)(r0 + q0) * H * KR, KR, rows, KR, cb, true, 1, 0, 0, 0, false));
@@ -961,6 +967,7 @@ int ssdk_hyb_create(const ssdk_hyb_cfg* cfg, const ssdk_hyb_layer_cfg* layers, s
   e->use_tc = env_int("SSDK_HYB_TCGEN05", 1) != 0;
   e->use_decode_attn = env_int("SSDK_HYB_DECODE_ATTN", 1) != 0;
   e->use_decode_mma = env_int("SSDK_HYB_DECODE_MMA", 1) != 0;
+  e->use_tc_scores = env_int("SSDK_HYB_TC_SCORES", 1) != 0;
   e->layers.resize(cfg->n_layers);
   for (int i = 0; i < cfg->n_layers; ++i) e->layers[i].c = layers[i];
   if (hyb_derive(e) != 0) { delete e; return -1; }
