@@ -104,13 +104,14 @@ static int get_encode() {
   g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
   return 0;
 }
-// bf16 row-major [rows, cols] matrix, box = [box_rows, 64 cols], 128B swizzle
-static int make_tmap(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t cols, int box_rows) {
+// bf16 row-major [rows, cols] matrix with `ld` elements between rows (0: dense), box = [box_rows, 64 cols], 128B swizzle
+static int make_tmap(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t cols, int box_rows, int64_t ld = 0) {
   CKI(get_encode());
-  if (cols % 8 != 0) return fail("TMA: row length %lld not a multiple of 8 elements", (long long)cols);
+  if (ld == 0) ld = cols;
+  if (cols % 8 != 0 || ld % 8 != 0 || ld < cols) return fail("TMA: row length %lld (stride %lld) not a multiple of 8 elements", (long long)cols, (long long)ld);
   if (((uintptr_t)ptr & 15) != 0) return fail("TMA: base pointer not 16-byte aligned");
   cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
+  cuuint64_t gstride[1] = {(cuuint64_t)ld * 2};
   cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,

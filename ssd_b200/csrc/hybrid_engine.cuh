@@ -39,6 +39,8 @@ struct ssdk_hyb_engine {
   void *h = nullptr, *h2 = nullptr, *mixes = nullptr, *t0 = nullptr, *t1 = nullptr;
   // latent attention: concatenated queries, one sequence's gathered keys / transposed latents, score and weight blocks
   void *qcat = nullptr, *keys = nullptr, *lat_t = nullptr, *att_p = nullptr; float* att_s = nullptr;
+  float* att_o = nullptr;    // fp32 P C of the latent-attention portions when it runs on the tcgen05 GEMM (rounded to T afterwards)
+  int w_lat_o = 0;           // heads x kv_rank of the widest latent layer
   size_t att_elems = 0; int w_qcat = 0, w_key = 0, w_kr = 0, w_lh = 0;
   float *rz = nullptr, *wts = nullptr, *eg = nullptr, *eo = nullptr, *sz = nullptr, *so = nullptr;
   void *ey = nullptr, *sy = nullptr;
@@ -56,15 +58,15 @@ struct ssdk_hyb_engine {
   bool use_decode_attn = true;  // fused single-token latent attention (SSDK_HYB_DECODE_ATTN=0: GEMM path for every row)
   bool use_tc_scores = true;    // score GEMM of latent-attention portions on the tcgen05 GEMM (SSDK_HYB_TC_SCORES=0: mma.sync tile)
   bool use_decode_mma = true;   // its tensor-core form for bf16 storage (SSDK_HYB_DECODE_MMA=0: the CUDA-core form)
-  std::map<std::tuple<const void*, int64_t, int, int>, CUtensorMap> tmaps;
+  std::map<std::tuple<const void*, int64_t, int, int, int>, CUtensorMap> tmaps;
   float* partials = nullptr; size_t partial_floats = 0;
-  int tmap(const void* ptr, int64_t rows, int K, int box_rows, const CUtensorMap** out) {
-    auto key = std::make_tuple(ptr, rows, K, box_rows);
+  int tmap(const void* ptr, int64_t rows, int K, int box_rows, const CUtensorMap** out, int ld = 0) {
+    auto key = std::make_tuple(ptr, rows, K, box_rows, ld);
     auto it = tmaps.find(key);
     if (it == tmaps.end()) {
       if (tmaps.size() >= 8192) tmaps.clear();   // activations at changing offsets / row counts: keep the table bounded
       CUtensorMap tm;
-      CKI(make_tmap(&tm, ptr, rows, K, box_rows));
+      CKI(make_tmap(&tm, ptr, rows, K, box_rows, ld));
       it = tmaps.emplace(key, tm).first;
     }
     *out = &it->second;
@@ -130,7 +132,7 @@ static int hyb_derive(ssdk_hyb_engine* e) {
         up(e->w_p1, (long long)H * V);
       }
       up(e->w_qcat, (long long)H * (c.kv_rank + c.rot_dim)); up(e->w_key, (long long)c.kv_rank + c.rot_dim);
-      up(e->w_kr, c.kv_rank); up(e->w_lh, H);
+      up(e->w_kr, c.kv_rank); up(e->w_lh, H); up(e->w_lat_o, (long long)H * c.kv_rank);
       up(e->w_t0, std::max((long long)c.q_rank, (long long)H * c.kv_rank)); up(e->w_t1, std::max((long long)H * D, (long long)H * V));
     } else if (c.mixer == SSDK_MIX_RGLRU) {
       const int R = c.inner;
@@ -216,7 +218,7 @@ static int64_t hyb_carve(ssdk_hyb_engine* e, uint8_t* base) {
   e->mix_out = (float*)take(cap * g.width * 4);
   e->mix2 = (float*)take(e->any_pair ? cap * g.width * 4 : 0);
   {
-    const size_t ctx_pad = align_up((size_t)g.max_blocks_per_seq * g.block_size, 8);
+    const size_t ctx_pad = align_up((size_t)g.max_blocks_per_seq * g.block_size, 64);
     e->qcat = take(cap * e->w_qcat * es);
     e->keys = take(e->w_key ? ctx_pad * e->w_key * es : 0);
     e->lat_t = take(e->w_kr ? ctx_pad * e->w_kr * es : 0);
@@ -224,6 +226,7 @@ static int64_t hyb_carve(ssdk_hyb_engine* e, uint8_t* base) {
     e->att_elems = e->w_lh ? std::max((size_t)e->w_lh * ctx_pad, std::min(cap * e->w_lh * ctx_pad, (size_t)24 << 20)) : 0;
     e->att_s = (float*)take(e->att_elems * 4);
     e->att_p = take(e->att_elems * es);
+    e->att_o = (float*)take(es == 2 ? cap * e->w_lat_o * 4 : 0);
   }
   e->rz = (float*)take(cap * e->w_e * 4);
   e->wts = (float*)take(A * 4);
@@ -276,12 +279,12 @@ struct HybRun {
   }
   // dense bf16 product on the tcgen05 GEMM of gemm.cuh (swap-AB, TMA-fed, fp32 out): K a multiple of 64, dense rows
   bool tc_ok(const void* A, int lda, const void* W, int ldw, int ldc, int N, int K) const {
-    return std::is_same<T, bf16>::value && e->use_tc && K % kBlockK == 0 && lda == K && ldw == K && ldc == N &&
+    return std::is_same<T, bf16>::value && e->use_tc && K % kBlockK == 0 && lda == K && ldw >= K && ldw % 8 == 0 && ldc == N &&
            ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0;
   }
-  int lin_tc(const void* A, const void* W, float* C, int m_total, int N, int K) {
+  int lin_tc(const void* A, const void* W, float* C, int m_total, int N, int K, int ldw) {
     const CUtensorMap* tm;   // (copied: a later lookup may empty the table)
-    CKI(e->tmap(W, N, K, 64, &tm));
+    CKI(e->tmap(W, N, K, 64, &tm, ldw == K ? 0 : ldw));
     const CUtensorMap tmW = *tm;
     // one launch for all rows: chunks of `un` tokens along gridDim.z share the weight tiles through L2
     const int un = umma_n_for(std::min(m_total, kMaxTokens)), chunks = (m_total + un - 1) / un;
@@ -307,7 +310,7 @@ struct HybRun {
   // C[M, N] (fp32 unless out_t) = A[M, K] W[N, K]^T
   int lin(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int m, int N, int K, bool out_t = false,
           int batch = 1, long long sA = 0, long long sW = 0, long long sC = 0, bool allow_tc = true) {
-    if (allow_tc && !out_t && batch == 1 && tc_ok(A, lda, W, ldw, ldc, N, K)) return lin_tc(A, W, (float*)C, m, N, K);
+    if (allow_tc && !out_t && batch == 1 && tc_ok(A, lda, W, ldw, ldc, N, K)) return lin_tc(A, W, (float*)C, m, N, K, ldw);
     ssdk::LinearArgs a = {};
     a.A = A; a.W = W; a.C = C; a.M = m; a.N = N; a.K = K; a.lda = lda; a.ldw = ldw; a.ldc = ldc;
     a.sA = sA; a.sW = sW; a.sC = sC;
@@ -510,20 +513,31 @@ struct HybRun {
         }
       }
     }
+    // both attention GEMMs of a portion run on the tcgen05 GEMM when the operands are whole k-blocks: the key count is then
+    // padded to 64 (zero keys, zero weights) instead of 8
+    const bool tc_attn = !kF32 && e->use_tc && e->use_tc_scores;
+    const int kpad = tc_attn ? 64 : 8;
     for (int s = 0; s < rg.n_seqs; ++s) {
-      const int r0 = h_cu[s], n = h_cu[s + 1] - r0, p0 = h_pos0[s], ctx = p0 + n, ctx_pad = (ctx + 7) / 8 * 8;
+      const int r0 = h_cu[s], n = h_cu[s + 1] - r0, p0 = h_pos0[s], ctx = p0 + n, ctx_pad = (ctx + kpad - 1) / kpad * kpad;
       if (fused_decode && n == 1) continue;
       CKI(L.go(ssdk::latent_gather_kernel<T>, dim3(ctx_pad), dim3(128), 0, (const T*)pool, (T*)e->keys, (T*)e->lat_t, rg, s, ctx, ctx_pad,
                KR, Wd));
       const int qb = (int)std::max<size_t>(1, e->att_elems / ((size_t)H * ctx_pad));
       for (int q0 = 0; q0 < n; q0 += qb) {
-        const int nq = std::min(qb, n - q0), rows = nq * H, cb = (p0 + q0 + nq + 7) / 8 * 8;  // keys this block can see, padded
+        const int nq = std::min(qb, n - q0), rows = nq * H, cb = (p0 + q0 + nq + kpad - 1) / kpad * kpad;  // keys this block can see, padded
         const T* qrows = (const T*)e->qcat + (size_t)(r0 + q0) * H * Wd;
-        // scores on the tcgen05 GEMM when the row is whole k-blocks (keys are the 128-row operand, (query, head) rows the tokens)
-        CKI(lin(qrows, Wd, e->keys, Wd, e->att_s, cb, rows, cb, Wd, false, 1, 0, 0, 0, e->use_tc_scores));
+        // scores: keys are the 128-row operand, (query, head) rows the tokens
+        CKI(lin(qrows, Wd, e->keys, Wd, e->att_s, cb, rows, cb, Wd, false, 1, 0, 0, 0, tc_attn));
         CKI(L.go(ssdk::sink_softmax_kernel<T>, dim3(rows), dim3(256), 0, (const float*)e->att_s, (T*)e->att_p,
                  (const T*)sink, H, cb, p0 + q0, c.attn_scale, rows, 0.f));
-        CKI(lin(e->att_p, cb, e->lat_t, ctx_pad, (T*)e->t0 + (size_t)(r0 + q0) * H * KR, KR, rows, KR, cb, true, 1, 0, 0, 0, false));
+        T* o_rows = (T*)e->t0 + (size_t)(r0 + q0) * H * KR;
+        if (tc_attn && tc_ok(e->att_p, cb, e->lat_t, ctx_pad, KR, KR, cb)) {
+          // P C: the transposed latents [kv_rank, ctx_pad] are the 128-row operand, read with the row stride of the gather
+          CKI(lin_tc(e->att_p, e->lat_t, e->att_o, rows, KR, cb, ctx_pad));
+          CKI(L.go(ssdk::cast_cols_kernel<T>, dim3(rows), dim3(128), 0, (const float*)e->att_o, KR, o_rows, KR, KR));
+        } else {
+          CKI(lin(e->att_p, cb, e->lat_t, ctx_pad, o_rows, KR, rows, KR, cb, true, 1, 0, 0, 0, false));
+        }
       }
     }
     // per-head value projection of the latent output, rounded to T for the output projection (after the sigmoid gate on
