@@ -65,6 +65,15 @@ struct GemmParams {
   unsigned* sk_counters;  // [tiles] arrival tickets, zero on entry and on exit
   int sk_width;           // row width of the partial buffer (N, or 2 * ffn for gate|up)
   PublishParams pub;      // EPI_PUBLISH only
+  // grouped mode (EPI_PARTIAL, g_tile_expert != nullptr): blockIdx.z indexes a device-side list of row tiles, each of one
+  // expert: tile t multiplies the rows g_tile_row0[t] .. + g_tile_rows[t] (<= UMMA_N) of the X map, whose rows are sorted by
+  // expert, with the weight rows of expert g_tile_expert[t] (g_expert_rows rows of the stacked W map per expert).  CTAs
+  // beyond *g_n_tiles leave at once.  Rows of the X box that belong to the next expert are multiplied and dropped.
+  const int* g_tile_expert = nullptr;
+  const int* g_tile_row0 = nullptr;
+  const int* g_tile_rows = nullptr;
+  const int* g_n_tiles = nullptr;
+  int g_expert_rows = 0;
 };
 
 // Split-K ticket reduction run by the 4 epilogue warps (threads 64..191).  `col` = this thread's column in the partial
@@ -143,11 +152,19 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const int tile = blockIdx.x;
   const int kb0 = blockIdx.y * p.kb_per_split;
   const int nkb = min(p.kb_per_split, p.num_kb - kb0);
-  const int row_lo = (EPI == EPI_SILU) ? tile * 64 : tile * kTileRows;
-  const int row_hi = row_lo + p.hi_row_offset;
   // row chunk (prefill-sized EPI_PARTIAL calls): this CTA multiplies tokens m_base .. m_base + m_valid of the X map
-  const int m_base = (int)blockIdx.z * UMMA_N;
-  const int m_valid = min(UMMA_N, p.M - m_base);
+  int m_base = (int)blockIdx.z * UMMA_N;
+  int m_valid = min(UMMA_N, p.M - m_base);
+  int w_row0 = 0;   // first weight row of this CTA's expert in the stacked W map (grouped mode)
+  if (EPI == EPI_PARTIAL && p.g_tile_expert != nullptr) {
+    if ((int)blockIdx.z >= *p.g_n_tiles) return;   // the whole CTA, before any barrier or TMEM allocation
+    m_base = p.g_tile_row0[blockIdx.z];
+    m_valid = min(UMMA_N, p.g_tile_rows[blockIdx.z]);
+    w_row0 = p.g_tile_expert[blockIdx.z] * p.g_expert_rows;
+  }
+  const int col_lo = (EPI == EPI_SILU) ? tile * 64 : tile * kTileRows;   // first output column of the tile
+  const int row_lo = col_lo + w_row0;                                    // its first weight row in the W map
+  const int row_hi = row_lo + p.hi_row_offset;
 
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmW);
@@ -248,7 +265,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           if (m0 + m < p.M) out[(size_t)(m0 + m) * p.ldo + n] = f2bf(__uint_as_float(r[m]));
       }
     } else if (EPI == EPI_PARTIAL) {
-      const int n = row_lo + row;
+      const int n = col_lo + row;
       if (n < p.N) {
         float* out = reinterpret_cast<float*>(p.out) + ((size_t)blockIdx.y * p.M + m_base) * p.N;
 #pragma unroll

@@ -43,7 +43,7 @@ struct ssdk_hyb_engine {
   int w_lat_o = 0;           // heads x kv_rank of the widest latent layer
   size_t att_elems = 0; int w_qcat = 0, w_key = 0, w_kr = 0, w_lh = 0;
   float *rz = nullptr, *wts = nullptr, *eg = nullptr, *eo = nullptr, *sz = nullptr, *so = nullptr;
-  void *ey = nullptr, *sy = nullptr;
+  void *ey = nullptr, *sy = nullptr, *xs = nullptr;   // xs: routed rows gathered per expert (grouped tcgen05 GEMM)
   int *sel = nullptr, *apos = nullptr, *arow = nullptr, *tile_expert = nullptr, *tile_row0 = nullptr, *tile_rows = nullptr,
       *n_tiles = nullptr, *n_rows = nullptr;
   void* hn = nullptr; float* logits = nullptr; bf16* logits16 = nullptr; int64_t* tokens = nullptr; float* temps = nullptr;
@@ -56,6 +56,7 @@ struct ssdk_hyb_engine {
   // tcgen05 path of the dense bf16 products: TMA descriptors by (pointer, rows, K, box rows), split-K partials
   bool use_tc = true;
   bool use_decode_attn = true;  // fused single-token latent attention (SSDK_HYB_DECODE_ATTN=0: GEMM path for every row)
+  bool use_tc_experts = true;   // routed experts of calls with many rows on the grouped tcgen05 GEMM (SSDK_HYB_TC_EXPERTS=0: mma.sync tile)
   bool use_tc_scores = true;    // score GEMM of latent-attention portions on the tcgen05 GEMM (SSDK_HYB_TC_SCORES=0: mma.sync tile)
   bool use_decode_mma = true;   // its tensor-core form for bf16 storage (SSDK_HYB_DECODE_MMA=0: the CUDA-core form)
   std::map<std::tuple<const void*, int64_t, int, int, int>, CUtensorMap> tmaps;
@@ -237,6 +238,7 @@ static int64_t hyb_carve(ssdk_hyb_engine* e, uint8_t* base) {
   e->n_tiles = (int*)take(4); e->n_rows = (int*)take(4);
   e->eg = (float*)take(A * e->w_ff2 * 4);
   e->ey = take(A * e->w_ff * es);
+  e->xs = take(es == 2 && e->w_e ? A * g.width * es : 0);
   e->eo = (float*)take(e->w_e ? A * g.width * 4 : 0);
   e->sz = (float*)take(cap * e->w_sff2 * 4);
   e->sy = take(cap * e->w_sff * es);
@@ -306,6 +308,21 @@ struct HybRun {
       CKI(L.go(ssdk::splitk_sum_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (const float*)e->partials, C, S, n));
     }
     return 0;
+  }
+  // grouped form: rows of X sorted by expert, tile list on the device (expert_plan_kernel with tiles of `un` rows);
+  // C[r, :] = X[r, :] Wm[expert(r)]^T with Wm the experts' [N, K] matrices stacked by rows
+  int lin_tc_grouped(const void* X, const void* Wm, float* C, int rows, int N, int K, int n_experts, int un, int max_tiles) {
+    const CUtensorMap* tm;
+    CKI(e->tmap(Wm, (int64_t)n_experts * N, K, 64, &tm));
+    const CUtensorMap tmW = *tm;
+    CKI(e->tmap(X, rows, K, un, &tm));
+    const CUtensorMap tmX = *tm;
+    GemmParams p;
+    p.M = rows; p.N = N; p.ldo = N; p.num_kb = K / kBlockK; p.kb_per_split = p.num_kb; p.tile_rows = kTileRows; p.hi_row_offset = 64;
+    p.sk_partials = nullptr; p.sk_counters = nullptr; p.sk_width = 0; p.out = C;
+    p.g_tile_expert = e->tile_expert; p.g_tile_row0 = e->tile_row0; p.g_tile_rows = e->tile_rows; p.g_n_tiles = e->n_tiles;
+    p.g_expert_rows = N;
+    return launch_gemm(L, un, EPI_PARTIAL, tmW, tmX, p, (N + kTileRows - 1) / kTileRows, 1, max_tiles);
   }
   // C[M, N] (fp32 unless out_t) = A[M, K] W[N, K]^T
   int lin(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int m, int N, int K, bool out_t = false,
@@ -565,24 +582,39 @@ struct HybRun {
     ra.top = top; ra.groups = c.groups; ra.keep = c.keep; ra.softmax = c.route_softmax; ra.group_best = c.group_best;
     ra.renorm = c.route_renorm; ra.route_scale = c.route_scale;
     CKI(L.go(ssdk::group_topk_router_kernel<T>, dim3((M + ssdk::kRouterWarps - 1) / ssdk::kRouterWarps), dim3(ssdk::kRouterWarps * 32), 0, ra));
+    // many rows in bf16 with whole k-blocks: the grouped tcgen05 GEMM over rows gathered per expert (tiles of 128 rows);
+    // else the mma.sync / FMA tile, which gathers by index itself (tiles of kLinBM rows)
+    const bool tc_moe = !kF32 && e->use_tc && e->use_tc_experts && A >= 256 && W % kBlockK == 0 && ff % kBlockK == 0 &&
+                        (((uintptr_t)Lr.t[SSDK_HT_EXPERT_IN].p | (uintptr_t)Lr.t[SSDK_HT_EXPERT_OUT].p) & 15) == 0;
+    const int tile = tc_moe ? 128 : ssdk::kLinBM;
     ssdk::PlanArgs pa;
     pa.sel = e->sel; pa.apos = e->apos; pa.arow = e->arow; pa.tile_expert = e->tile_expert; pa.tile_row0 = e->tile_row0;
-    pa.tile_rows = e->tile_rows; pa.n_tiles = e->n_tiles; pa.n_rows = e->n_rows; pa.A = A; pa.E = Et; pa.top = top; pa.tile = ssdk::kLinBM;
+    pa.tile_rows = e->tile_rows; pa.n_tiles = e->n_tiles; pa.n_rows = e->n_rows; pa.A = A; pa.E = Et; pa.top = top; pa.tile = tile;
     pa.E_real = E;
     CKI(L.go(ssdk::expert_plan_kernel, dim3(1), dim3(1024), 0, pa));
-    ssdk::LinearArgs a = {};
-    a.A = fin; a.W = Lr.t[SSDK_HT_EXPERT_IN].p; a.C = e->eg; a.M = A; a.N = 2 * ff; a.K = W; a.lda = W; a.ldw = W; a.ldc = 2 * ff;
-    a.a_rows = e->arow; a.tile_expert = e->tile_expert; a.tile_row0 = e->tile_row0; a.tile_rows = e->tile_rows; a.n_tiles = e->n_tiles;
-    a.sW_expert = (long long)2 * ff * W;
-    CKI(lin_args<float>(a, A, 1));
     const int* n_real_rows = c.identity > 0 ? e->n_rows : nullptr;   // rows behind them belong to identity experts: nothing to compute
+    ssdk::LinearArgs a = {};
+    if (tc_moe) {
+      CKI(L.go(ssdk::gather_rows_kernel<T>, dim3(A), dim3(128), 0, (const T*)fin, (const int*)e->arow, (const int*)e->n_rows, (T*)e->xs, W));
+      CKI(lin_tc_grouped(e->xs, Lr.t[SSDK_HT_EXPERT_IN].p, e->eg, A, 2 * ff, W, E, tile, A / tile + E + 1));
+    } else {
+      a.A = fin; a.W = Lr.t[SSDK_HT_EXPERT_IN].p; a.C = e->eg; a.M = A; a.N = 2 * ff; a.K = W; a.lda = W; a.ldw = W; a.ldc = 2 * ff;
+      a.a_rows = e->arow; a.tile_expert = e->tile_expert; a.tile_row0 = e->tile_row0; a.tile_rows = e->tile_rows; a.n_tiles = e->n_tiles;
+      a.sW_expert = (long long)2 * ff * W;
+      CKI(lin_args<float>(a, A, 1));
+    }
     if (c.expert_act == SSDK_ACT_SILU)
       CKI(L.go(ssdk::glu_act_kernel<T, SSDK_ACT_SILU>, dim3(A), dim3(128), 0, (const float*)e->eg, 2 * ff, (T*)e->ey, ff, n_real_rows));
     else
       CKI(L.go(ssdk::clamped_glu_kernel<T>, dim3(A), dim3(128), 0, (const float*)e->eg, 2 * ff, (T*)e->ey, ff, c.limit, n_real_rows));
-    a.A = e->ey; a.W = Lr.t[SSDK_HT_EXPERT_OUT].p; a.C = e->eo; a.N = W; a.K = ff; a.lda = ff; a.ldw = ff; a.ldc = W; a.a_rows = nullptr;
-    a.sW_expert = (long long)W * ff;
-    CKI(lin_args<float>(a, A, 1));
+    if (tc_moe) {
+      CKI(lin_tc_grouped(e->ey, Lr.t[SSDK_HT_EXPERT_OUT].p, e->eo, A, W, ff, E, tile, A / tile + E + 1));
+    } else {
+      a.A = e->ey; a.W = Lr.t[SSDK_HT_EXPERT_OUT].p; a.C = e->eo; a.N = W; a.K = ff; a.lda = ff; a.ldw = ff; a.ldc = W; a.a_rows = nullptr;
+      a.tile_expert = e->tile_expert; a.tile_row0 = e->tile_row0; a.tile_rows = e->tile_rows; a.n_tiles = e->n_tiles;
+      a.M = A; a.sW_expert = (long long)W * ff;
+      CKI(lin_args<float>(a, A, 1));
+    }
     if (c.shared_ff > 0) {
       const int sff = c.shared_ff, Ns = 2 * sff + (c.shared_gate ? 1 : 0);
       CKI(check_tensor(Lr, SSDK_HT_SHARED_IN, Ns, W, "shared.in")); CKI(check_tensor(Lr, SSDK_HT_SHARED_OUT, W, sff, "shared.out"));
@@ -982,6 +1014,7 @@ int ssdk_hyb_create(const ssdk_hyb_cfg* cfg, const ssdk_hyb_layer_cfg* layers, s
   e->use_decode_attn = env_int("SSDK_HYB_DECODE_ATTN", 1) != 0;
   e->use_decode_mma = env_int("SSDK_HYB_DECODE_MMA", 1) != 0;
   e->use_tc_scores = env_int("SSDK_HYB_TC_SCORES", 1) != 0;
+  e->use_tc_experts = env_int("SSDK_HYB_TC_EXPERTS", 1) != 0;
   e->layers.resize(cfg->n_layers);
   for (int i = 0; i < cfg->n_layers; ++i) e->layers[i].c = layers[i];
   if (hyb_derive(e) != 0) { delete e; return -1; }

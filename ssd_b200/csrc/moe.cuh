@@ -12,7 +12,8 @@
 //       (expert, first row, rows) that the grouped linear kernel walks — tiles are made for the first E_real outputs
 //       only; *n_rows = rows that belong to real experts (they come first).  The order of rows inside one expert is
 //       arbitrary; every row is computed independently, so results do not depend on it.
-// The expert matrices themselves run through linear_kernel in grouped mode (linear.cuh) and a GLU kernel.
+// The expert matrices themselves run through the grouped mode of the tcgen05 GEMM (bf16, many rows, whole k-blocks: rows first
+// made contiguous per expert by gather_rows_kernel) or of linear_kernel / linear_mma_kernel (linear.cuh), and a GLU kernel.
 #pragma once
 #include "layer_ops.cuh"
 
@@ -146,6 +147,22 @@ __global__ void __launch_bounds__(1024) expert_plan_kernel(const PlanArgs p) {
     const int row = s_off[e] + atomicAdd(&s_cnt[e], 1);
     p.apos[a] = row;
     p.arow[row] = a / p.top;
+  }
+}
+
+// dst[r, :] = src[rows[r], :] for r < *n_rows: the routed rows made contiguous per expert (operand of the grouped tcgen05 GEMM,
+// whose TMA boxes cannot follow an index list)
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restrict__ rows, const int* __restrict__ n_rows,
+                                   T* __restrict__ dst, int width) {
+  const int r = blockIdx.x;
+  if (r >= *n_rows) return;
+  const T* s = src + (size_t)rows[r] * width;
+  T* d = dst + (size_t)r * width;
+  if (sizeof(T) == 2 && width % 8 == 0 && (((uintptr_t)src | (uintptr_t)dst) & 15) == 0) {
+    for (int c = threadIdx.x; c < width / 8; c += blockDim.x) ((uint4*)d)[c] = ((const uint4*)s)[c];
+  } else {
+    for (int c = threadIdx.x; c < width; c += blockDim.x) d[c] = s[c];
   }
 }
 
