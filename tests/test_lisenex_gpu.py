@@ -334,6 +334,29 @@ def test_bfloat16_calls_of_many_rows(tmp_path):
     assert U.rel_err(np.concatenate(out), got[0]) < 2e-2
 
 
+def test_bfloat16_experts_on_the_grouped_tensor_core_gemm(tmp_path, monkeypatch):
+    """Calls with many routed rows take the grouped tcgen05 GEMM (rows gathered per expert, a tile list per expert on the
+    device): experts with few or no rows, identity outputs sorted behind the real ones, an output width that ends inside a
+    tile (the next expert's rows are read and dropped).  Against the mma.sync tile on the same checkpoint (the routing is the
+    same code, so the two agree to rounding) and, with every output chosen, against the oracle."""
+    for name, mlp, oracle in (("few", U.moe(experts=9, identity=1, top=2, groups=5, keep=2, ff=64, shared_ff=0), False),
+                              ("all", U.moe(experts=5, identity=1, top=6, groups=3, keep=3, ff=192, shared_ff=64), True)):
+        cfg = U.config([U.latent(heads=2, dim=16, rot_dim=16, vdim=16, kv_rank=48, mlp=mlp),
+                        U.latent(kv_from=0, heads=3, dim=8, rot_dim=16, vdim=8, kv_rank=48, mlp=mlp)], width=192)
+        tensors = U.random_tensors(cfg, 13, correction=1.0)
+        path = U.write_checkpoint(str(tmp_path / name), cfg, tensors)
+        toks = _tokens(300, cfg["vocab"], 120)
+        got = {}
+        for tc in ("1", "0"):
+            monkeypatch.setenv("SSDK_HYB_TC_EXPERTS", tc)
+            r = _load(path, "bfloat16", num_blocks=24)
+            got[tc], _ = r.forward([(toks, 0, 0, _pages(300, 16), list(range(300)))])
+            r.close()
+        assert U.rel_err(got["1"], got["0"]) < 2e-3, name
+        if oracle:
+            assert U.rel_err(got["1"], PlainModel(cfg, tensors).run(toks).numpy()) < BF16_TOL
+
+
 def test_greedy_generation_through_llm(tmp_path):
     """The public entry point: LLM.generate with the engine's scheduler (three prompts, two sequences at a time: the third
     waits and gets used pages), temperature 0, against the oracle's greedy continuation."""
