@@ -257,10 +257,11 @@ int ssdk_verify(const void* logits_p, const void* logits_q, const int64_t* specu
 /* ---- layered ("hybrid") models ---------------------------------------------------
  * A second model family beside the dense Llama / Qwen3 decoders above: a program of layers, each one token mixer
  * (a recurrent layer, latent attention, or grouped-query attention beside a delta rule) and an optional feed-forward.
- * Three block kinds (SSDK_BLOCK_*): mixer and mixture of experts read the SAME normed input and join the residual
+ * Block kinds (SSDK_BLOCK_*): mixer and mixture of experts read the SAME normed input and join the residual
  * stream through per-channel layer scales (parallel pre-norm); each sublayer reads the residual stream itself and
  * its OUTPUT is normed before it is added (serial post-norm); or mixer and feed-forward read the same residual row
- * through a norm weight of their own and are added unscaled (parallel, two norms).  The reference has no such model; these entry
+ * through a norm weight of their own and are added unscaled (parallel, two norms); or both read one plain norm's rows, each
+ * through a short input convolution of its own, and are gated per channel before they are added (parallel, one norm).  The reference has no such model; these entry
  * points follow the conventions of the ones above (caller-owned device memory, int return codes).
  * Storage type T of weights / activations / latent cache: bf16 (fp32 accumulation; residual stream, norms, routers,
  * attention scores, gates and recurrent state in fp32) or fp32 throughout (no TF32). */
@@ -268,15 +269,20 @@ enum { SSDK_DT_F32 = 0, SSDK_DT_BF16 = 1 };
 enum { SSDK_MIX_WKV = 0, SSDK_MIX_MLSTM = 1, SSDK_MIX_LATENT_ATTN = 2,
        SSDK_MIX_RGLRU = 3,        /* gated diagonal linear recurrence behind a short convolution, times a gelu branch */
        SSDK_MIX_SELECTIVE = 4,    /* selective scan (input-dependent step, B, C) behind a short convolution, silu gate */
-       SSDK_MIX_ATTN_DELTA = 5 }; /* grouped-query sink attention and a gated delta rule side by side on the same input */
+       SSDK_MIX_ATTN_DELTA = 5,   /* grouped-query sink attention and a gated delta rule side by side on the same input */
+       SSDK_MIX_ATTENTION = 6 };  /* grouped-query attention alone: biased q | k | v projections behind a short convolution,
+                                   * rotate-half rotation of the first rot_dims entries, optional sliding window, learned sink */
 enum { SSDK_MLP_NONE = 0, SSDK_MLP_MOE = 1, SSDK_MLP_GLU = 2, /* dense: down(gelu_tanh(gate h) * (up h)) */
        SSDK_MLP_FFN = 3 };        /* dense, not gated: down(act(up h + b_up)) + b_down, act = ff_act */
 /* activations of the feed-forward kernels; CLAMPED is the limited GLU g sigmoid(1.702 g) (u + 1) */
-enum { SSDK_ACT_CLAMPED = 0, SSDK_ACT_SILU = 1, SSDK_ACT_GELU_TANH = 2, SSDK_ACT_RELU2 = 3 /* relu(z)^2 */ };
+enum { SSDK_ACT_CLAMPED = 0, SSDK_ACT_SILU = 1, SSDK_ACT_GELU_TANH = 2, SSDK_ACT_RELU2 = 3, /* relu(z)^2 */
+       SSDK_ACT_POLYNORM = 4 };   /* k1 u1 + k2 u2 + k3 u3 + k0 with u_p = z^p / rms(z^p) over the row; SSDK_HT_FFN_ACT holds k1, k2, k3, k0 */
 /* how a layer joins the residual stream */
 enum { SSDK_BLOCK_PARALLEL_PRENORM = 0,  /* x += ls1 * mixer(h) + ls2 * ff(h), h = norm(x) */
        SSDK_BLOCK_SERIAL_POSTNORM = 1,   /* x += m * norm1(mixer(x)); x += m * norm2(ff(x)): the sublayers read x itself */
-       SSDK_BLOCK_PARALLEL_TWO_NORMS = 2 }; /* x += mixer(norm1(x)) + ff(norm2(x)): one statistic, two weights, no layer scales */
+       SSDK_BLOCK_PARALLEL_TWO_NORMS = 2, /* x += mixer(norm1(x)) + ff(norm2(x)): one statistic, two weights, no layer scales */
+       SSDK_BLOCK_PARALLEL_ONE_NORM = 3 }; /* h = norm(x); x += g1 * mixer(h + conv1(h)) + g2 * ff(h + conv2(h)): plain norm weight; the
+                                            * input convolutions (canon_taps > 0) and the gates g = sigmoid(W_g h + b) (gated_residual) are optional */
 
 /* tensors of a hybrid model (ssdk_hyb_bind); [out, in] row-major, storage type T */
 enum {
@@ -348,6 +354,16 @@ enum {
   SSDK_HT_FFN_OUT,       /* [width, ff] */
   SSDK_HT_FFN_OUT_B,     /* [width] */
   SSDK_HT_ROUTER_BIAS,   /* [E + identity] added to the scores for the CHOICE of experts only (route_bias) */
+  /* grouped-query attention alone (SSDK_MIX_ATTENTION): ONE stacked input projection q [H D] | k [G D] | v [G V], its bias,
+   * the per-channel taps of the convolution that follows it (SSDK_HT_CONV_W, same row order) and one sink logit per head */
+  SSDK_HT_ATTN_IN,       /* [H D + G D + G V, width] */
+  SSDK_HT_ATTN_IN_B,     /* [H D + G D + G V] or unbound */
+  SSDK_HT_ATTN_SINK,     /* [H] (learned_sink) */
+  SSDK_HT_FFN_ACT,       /* [4] coefficients k1, k2, k3, k0 of SSDK_ACT_POLYNORM */
+  /* SSDK_BLOCK_PARALLEL_ONE_NORM */
+  SSDK_HT_CANON_W,       /* [2, width, canon_taps]: taps of the mixer's input convolution, then of the feed-forward's */
+  SSDK_HT_RES_GATE,      /* [2 width, width]: rows of the mixer's residual gate, then of the feed-forward's */
+  SSDK_HT_RES_GATE_B,    /* [2 width] */
   SSDK_HT_COUNT
 };
 
@@ -389,6 +405,11 @@ typedef struct ssdk_hyb_layer_cfg {
   int32_t route_renorm;              /* 1: the chosen scores are divided by their sum */
   int32_t expert_act, shared_gate;   /* SSDK_ACT_CLAMPED | SSDK_ACT_SILU; 1: the shared expert is scaled by sigmoid of its gate row */
   int32_t ff_act;                    /* SSDK_MLP_FFN: SSDK_ACT_* */
+  int32_t window;                    /* attention (latent or grouped-query): a query at position p reads the keys at p - window + 1 .. p; 0: all of 0 .. p */
+  int32_t rot_half;                  /* SSDK_MIX_ATTENTION: 1 = entry i turns with i + rot_dims/2, 0 = entry 2i with 2i + 1 */
+  int32_t expert_glu;                /* 1: experts are down(act(gate h) * (up h)), SSDK_HT_EXPERT_IN / SHARED_IN hold gate | up rows;
+                                      * 0: down(act(up h)), they hold the up rows only */
+  int32_t route_top_softmax;         /* 1: the choice is made on the raw logits and the weights are the softmax over the chosen logits */
 } ssdk_hyb_layer_cfg;
 
 typedef struct ssdk_hyb_cfg {
@@ -402,6 +423,8 @@ typedef struct ssdk_hyb_cfg {
   float   norm_offset;       /* a norm scales by norm_offset + w: 1 for unit-offset weights, 0 for plain ones */
   float   embed_scale;       /* x = embed[token] * embed_scale */
   float   residual_mult;     /* m of SSDK_BLOCK_SERIAL_POSTNORM */
+  int32_t canon_taps;        /* SSDK_BLOCK_PARALLEL_ONE_NORM: taps of the sublayers' input convolutions (0: none) */
+  int32_t gated_residual;    /* SSDK_BLOCK_PARALLEL_ONE_NORM: 1 = each sublayer's result is multiplied by sigmoid(W_g h + b) */
 } ssdk_hyb_cfg;
 
 typedef struct ssdk_hyb_engine* ssdk_hyb_handle;
@@ -410,7 +433,7 @@ int ssdk_hyb_create(const ssdk_hyb_cfg* cfg, const ssdk_hyb_layer_cfg* layers, s
 int ssdk_hyb_destroy(ssdk_hyb_handle h);
 int ssdk_hyb_bind(ssdk_hyb_handle h, int layer, int tensor, const void* dev_ptr, int64_t rows, int64_t cols);
 /* caller-owned pools: paged cache (per latent-attention layer [num_blocks, block_size, kv_rank + rot_dim] T, per
- * grouped-query attention layer [num_blocks, block_size, G (D + V)] T: keys of all heads, then values; layers back to back), recurrent state (fp32, n_slots slots), workspace */
+ * grouped-query attention layer (SSDK_MIX_ATTN_DELTA, SSDK_MIX_ATTENTION) [num_blocks, block_size, G (D + V)] T: keys of all heads, then values; layers back to back), recurrent state (fp32, n_slots slots), workspace */
 int64_t ssdk_hyb_cache_bytes(ssdk_hyb_handle h, int64_t num_blocks);
 int64_t ssdk_hyb_state_bytes(ssdk_hyb_handle h, int64_t n_slots);
 int64_t ssdk_hyb_workspace_bytes(ssdk_hyb_handle h);

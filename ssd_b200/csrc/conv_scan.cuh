@@ -6,6 +6,8 @@
 //                         optional input bias / output bias / SiLU; rows before the portion come from the state slot,
 //                         zeros before the sequence
 //   conv_state_kernel     saves the last taps - 1 inputs of every sequence's portion into its slot (runs after the readers)
+//   input_conv_kernel     a block's input convolutions: y_k = h + conv_k(h) for up to two tap sets over the same rows h (T),
+//                         no bias; input_conv_state_kernel saves the last taps - 1 rows of h
 //   rglru_scan_kernel     S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t,  a_t = exp(-c r_t softplus(lam)),  out = S_t gelu(y_t)
 //   selective_scan_kernel S[c,n] = exp(dt_c A[c,n]) S[c,n] + dt_c x_c B_n,  y_c = sum_n S[c,n] C_n + D_c x_c,  out = y silu(z)
 //   delta_prep_kernel     convolution + SiLU of q | k | v, unit vectors per head for q and k, beta and the head decay
@@ -81,6 +83,62 @@ __global__ void conv_state_kernel(const ConvArgs p, const Ragged rg) {
     float v;
     if (idx < keep) v = carried ? hist[(size_t)idx * p.C + c] : 0.f;
     else v = p.in[(size_t)(r0 + idx - keep) * p.ld_in + c] + ib;
+    hist[(size_t)j * p.C + c] = v;
+  }
+}
+
+// Residual input convolution of a block's sublayers.  h [M, C] (T) are the rows both sublayers read; sublayer k gets
+// y_k[m, c] = h[m, c] + sum_j w_k[c, j] h[row of position t - taps + 1 + j, c] with zeros before the sequence's start and the
+// rows before the portion taken from the state slot (hist [taps - 1, C] fp32 per slot, oldest first).  Sums in fp32.
+struct InputConvArgs {
+  const void* h;        // [M, C] T
+  const void* w;        // [2, C, taps] T: taps of y1, then of y2
+  void* y1;             // [M, C] T
+  void* y2;             // [M, C] T or nullptr
+  float* hist; size_t slot_stride;
+  int C, taps;
+};
+
+// grid (M, ceil(C / blockDim))
+template <typename T>
+__global__ void input_conv_kernel(const InputConvArgs p, const Ragged rg) {
+  const int m = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= p.C) return;
+  const int s = rg.tok_seq[m], t = m - rg.cu[s];
+  const bool carried = rg.pos0[s] > 0;
+  const float* hist = p.hist + (size_t)rg.slot[s] * p.slot_stride;
+  const T* h = (const T*)p.h;
+  const T* w1 = (const T*)p.w + (size_t)c * p.taps;
+  const T* w2 = w1 + (size_t)p.C * p.taps;
+  const float cur = ld_f<T>(h + (size_t)m * p.C + c);
+  float a1 = 0.f, a2 = 0.f;
+  for (int j = 0; j < p.taps; ++j) {
+    const int back = p.taps - 1 - j;
+    float v;
+    if (back == 0) v = cur;
+    else if (back <= t) v = ld_f<T>(h + (size_t)(m - back) * p.C + c);
+    else v = carried ? hist[(size_t)(p.taps - 1 - (back - t)) * p.C + c] : 0.f;
+    a1 = fmaf(ld_f<T>(w1 + j), v, a1);
+    if (p.y2) a2 = fmaf(ld_f<T>(w2 + j), v, a2);
+  }
+  st_f<T>((T*)p.y1 + (size_t)m * p.C + c, cur + a1);
+  if (p.y2) st_f<T>((T*)p.y2 + (size_t)m * p.C + c, cur + a2);
+}
+
+// grid (n_seqs, ceil(C / blockDim)); runs after input_conv_kernel.  As conv_state_kernel: entry j is read from an index
+// above j, so one thread per channel works in place in ascending order.
+template <typename T>
+__global__ void input_conv_state_kernel(const InputConvArgs p, const Ragged rg) {
+  const int s = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= p.C) return;
+  const int r0 = rg.cu[s], n = rg.cu[s + 1] - r0, keep = p.taps - 1;
+  const bool carried = rg.pos0[s] > 0;
+  float* hist = p.hist + (size_t)rg.slot[s] * p.slot_stride;
+  for (int j = 0; j < keep; ++j) {
+    const int idx = n + j;
+    float v;
+    if (idx < keep) v = carried ? hist[(size_t)idx * p.C + c] : 0.f;
+    else v = ld_f<T>((const T*)p.h + (size_t)(r0 + idx - keep) * p.C + c);
     hist[(size_t)j * p.C + c] = v;
   }
 }

@@ -2,9 +2,9 @@
 // models.  H query heads share G key/value heads (query head h reads head h / (H / G)); key size D and value size V are
 // independent.  A page row holds, for one token, the keys of all G heads (rotated, optionally unit-RMS) and then their
 // values: [G D | G V] of storage type T.  The softmax denominator may carry a constant (`sink`: 1 = a sink of score 0
-// that has no value), on top of or instead of the learned per-head sink of latent attention.
+// that has no value) or a learned logit per query head; a sliding window limits a query to its last `window` positions.
 //
-//   gqa_prep_kernel      per (token, head): interleaved-pair rotation of the first rot_dims dimensions (angle = position *
+//   gqa_prep_kernel      per (token, head): rotation of the first rot_dims dimensions in adjacent or half-apart pairs (angle = position *
 //                        frequency in fp32, cos and sin times a constant), optional unit RMS over D; queries go to a
 //                        group-major buffer [G, M, H/G, D] (T), keys and raw values into the token's page row
 //   kv_gather_kernel     one sequence's pages -> contiguous keys [G, ctx_pad, D] and transposed values [G, V, ctx_pad]
@@ -24,6 +24,7 @@ struct GqaPrepArgs {
   const float* inv_freq;       // [rot_dims / 2] or nullptr
   int H, G, D, V, rot_dims, qk_norm;
   float rot_mult, eps;
+  int rot_half;                // 0: entry 2i turns with 2i + 1; 1: entry i turns with i + rot_dims / 2
 };
 
 // grid (M, H + G), one warp: units 0 .. H-1 are query heads, H .. H+G-1 key heads (which also copy their value head)
@@ -47,6 +48,13 @@ __global__ void gqa_prep_kernel(const GqaPrepArgs p, const Ragged rg) {
   const int rd = p.inv_freq ? p.rot_dims : 0;
   auto value = [&](int d) -> float {
     if (d >= rd) return src[d];
+    if (p.rot_half) {
+      const int half = rd >> 1, i = d < half ? d : d - half;
+      float sn, cs;
+      sincosf((float)pos * p.inv_freq[i], &sn, &cs);
+      sn *= p.rot_mult; cs *= p.rot_mult;
+      return d < half ? src[d] * cs - src[d + half] * sn : src[d] * cs + src[d - half] * sn;
+    }
     const int i = d >> 1;
     float sn, cs;
     sincosf((float)pos * p.inv_freq[i], &sn, &cs);
@@ -68,12 +76,12 @@ __global__ void gqa_prep_kernel(const GqaPrepArgs p, const Ragged rg) {
   }
 }
 
-// grid (ctx_pad): position j of sequence s -> keys[g][j][:] and vt[g][:][j]; zero from ctx up to ctx_pad
+// grid (ctx_pad): position lo + j of sequence s -> keys[g][j][:] and vt[g][:][j]; zero from ctx up to ctx_pad
 template <typename T>
 __global__ void kv_gather_kernel(const T* __restrict__ cache, T* __restrict__ keys, T* __restrict__ vt, const Ragged rg, int s,
-                                 int ctx, int ctx_pad, int G, int D, int V) {
+                                 int lo, int ctx, int ctx_pad, int G, int D, int V) {
   const int j = blockIdx.x;
-  const T* row = j < ctx ? cache + page_row(rg, s, j) * (size_t)(G * (D + V)) : nullptr;
+  const T* row = j < ctx ? cache + page_row(rg, s, lo + j) * (size_t)(G * (D + V)) : nullptr;
   for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
     const int g = i / D, d = i - g * D;
     keys[((size_t)g * ctx_pad + j) * D + d] = row ? row[i] : T(0.f);
@@ -88,6 +96,8 @@ struct GqaDecodeArgs {
   float* out;         // [G, M, H/G, V] fp32
   int H, G, D, V, splits;
   float scale, sink;
+  const void* sinks;  // [H] T learned sink logits (they replace the constant), or nullptr
+  int window;         // as LatentDecodeArgs::window
 };
 
 constexpr int kGqaDecWarps = 4;
@@ -142,8 +152,8 @@ __global__ void __launch_bounds__(kGqaDecWarps * 32) gqa_decode_partial_kernel(c
   const T* q = (const T*)p.q + (((size_t)g * rg.M + row) * hpg + (hd - g * hpg)) * D;
   for (int d = tid; d < Dp; d += blockDim.x) qs[d] = d < D ? ld_f<T>(q + d) * p.scale : 0.f;
   __syncthreads();
-  const int ctx = rg.pos0[s] + 1, per = (ctx + p.splits - 1) / p.splits;
-  const int k_lo = sp * per, k_hi = min(ctx, k_lo + per);
+  int k_lo, k_hi;
+  decode_split(rg.pos0[s] + 1, p.window, sp, p.splits, &k_lo, &k_hi);
   const size_t roww = (size_t)G * (D + V);
   constexpr int kPer = 16 / (int)sizeof(T);
   const bool pool16 = ((uintptr_t)p.cache & 15) == 0;
@@ -233,16 +243,19 @@ __global__ void __launch_bounds__(kGqaDecWarps * 32) gqa_decode_partial_kernel(c
   if (tid == 0) dst[V] = m;
 }
 
-// grid (n_seqs, H): out = sum_j e^(m_j - m) acc_j / (sink e^(-m) + sum_j e^(m_j - m) l_j)
+// grid (n_seqs, H): out = sum_j e^(m_j - m) acc_j / (e^(s - m) + sum_j e^(m_j - m) l_j), s the sink's logit (ln of the
+// constant, or the head's learned one)
+template <typename T>
 __global__ void gqa_decode_merge_kernel(const GqaDecodeArgs p, const Ragged rg) {
   const int s = blockIdx.x, hd = blockIdx.y;
   const int row = rg.cu[s];
   if (rg.cu[s + 1] - row != 1) return;
   const int V = p.V, hpg = p.H / p.G, g = hd / hpg;
   const float* part = p.part + ((size_t)s * p.H + hd) * p.splits * (V + 2);
-  float m = p.sink > 0.f ? 0.f : -INFINITY;
+  const float sk = p.sinks ? ld_f<T>((const T*)p.sinks + hd) : (p.sink > 0.f ? logf(p.sink) : -INFINITY);
+  float m = sk;
   for (int j = 0; j < p.splits; ++j) m = fmaxf(m, part[(size_t)j * (V + 2) + V]);
-  float den = p.sink > 0.f ? p.sink * expf(-m) : 0.f;
+  float den = sk == -INFINITY ? 0.f : expf(sk - m);
   for (int j = 0; j < p.splits; ++j) {
     const float mj = part[(size_t)j * (V + 2) + V];
     if (mj != -INFINITY) den += expf(mj - m) * part[(size_t)j * (V + 2) + V + 1];

@@ -19,6 +19,7 @@ struct HybLayer {
   ssdk_hyb_layer_cfg c;
   HybTensor t[SSDK_HT_COUNT];
   size_t state_off = 0;      // floats from the start of a slot
+  size_t canon_off = 0;      // one-norm blocks: the input convolutions' history [canon_taps - 1, width], floats from the start of a slot
   size_t cache_row = 0;      // row width (elements) of this layer's latent pool
   size_t cache_rows_before = 0;  // sum of the row widths of the latent layers before this one
   float* inv_freq = nullptr; // device, [rot_dims / 2]
@@ -36,7 +37,8 @@ struct ssdk_hyb_engine {
   // workspace carve
   int64_t ws_bytes = 0;
   float *x = nullptr, *p0 = nullptr, *p1 = nullptr, *p2 = nullptr, *mix_out = nullptr, *mix2 = nullptr;
-  void *h = nullptr, *h2 = nullptr, *mixes = nullptr, *t0 = nullptr, *t1 = nullptr;
+  void *h = nullptr, *h2 = nullptr, *hc = nullptr, *mixes = nullptr, *t0 = nullptr, *t1 = nullptr;
+  float* gz = nullptr;       // one-norm blocks: pre-activations of the two residual gates [rows, 2 width]
   // latent attention: concatenated queries, one sequence's gathered keys / transposed latents, score and weight blocks
   void *qcat = nullptr, *keys = nullptr, *lat_t = nullptr, *att_p = nullptr; float* att_s = nullptr;
   float* att_o = nullptr;    // fp32 P C of the latent-attention portions when it runs on the tcgen05 GEMM (rounded to T afterwards)
@@ -96,6 +98,13 @@ static int hyb_derive(ssdk_hyb_engine* e) {
     const ssdk_hyb_layer_cfg& c = L.c;
     const int H = c.heads, D = c.dim, V = c.vdim;
     if (H < 1 || D < 1) return fail("hybrid layer: heads / dim must be positive");
+    if (c.window < 0) return fail("hybrid layer: window %d", c.window);
+    if (g.block == SSDK_BLOCK_PARALLEL_ONE_NORM) {
+      if (c.mixer != SSDK_MIX_ATTENTION && c.mixer != SSDK_MIX_LATENT_ATTN && c.mixer != SSDK_MIX_RGLRU && c.mixer != SSDK_MIX_SELECTIVE)
+        return fail("one-norm blocks are built for the attention, latent-attention, rglru and selective-scan mixers");
+      L.canon_off = soff;
+      if (g.canon_taps > 1) soff += (size_t)(g.canon_taps - 1) * g.width;
+    }
     L.state_off = soff;
     if (c.mixer == SSDK_MIX_WKV) {
       if (D > 1024 || (size_t)(D * D + 5 * D + 1024) * 4 > 200 * 1024) return fail("wkv: head dim %d too large for the resident-state scan", D);
@@ -168,6 +177,19 @@ static int hyb_derive(ssdk_hyb_engine* e) {
       up(e->w_t0, (long long)H * V); up(e->w_t1, (long long)Hd * Vd);
       up(e->w_qcat, (long long)H * D); up(e->w_key, (long long)G * D); up(e->w_kr, (long long)G * V); up(e->w_lh, H);
       e->any_pair = true;
+    } else if (c.mixer == SSDK_MIX_ATTENTION) {
+      const int G = c.kv_heads;
+      if (V < 1 || G < 1 || H % G) return fail("attention: %d query heads on %d key/value heads", H, G);
+      if (c.rot_dims < 0 || c.rot_dims > D || (c.rot_dims & 1)) return fail("attention: rot dims %d of %d", c.rot_dims, D);
+      if (V > 256 * 4) return fail("attention: value size %d too large", V);
+      if (c.conv < 1) return fail("attention: %d taps", c.conv);
+      const long long Nqkv = (long long)H * D + (long long)G * D + (long long)G * V;
+      soff += (size_t)(c.conv - 1) * Nqkv;
+      L.cache_row = (size_t)G * (D + V);
+      L.cache_rows_before = crow;
+      crow += L.cache_row;
+      up(e->w_p0, Nqkv); up(e->w_p1, Nqkv); up(e->w_p2, (long long)H * V); up(e->w_t0, (long long)H * V);
+      up(e->w_qcat, (long long)H * D); up(e->w_key, (long long)G * D); up(e->w_kr, (long long)G * V); up(e->w_lh, H);
     } else {
       return fail("hybrid layer: unknown mixer %d", c.mixer);
     }
@@ -178,7 +200,8 @@ static int hyb_derive(ssdk_hyb_engine* e) {
     } else if (c.mlp == SSDK_MLP_FFN) {
       if (c.ff < 1) return fail("dense feed-forward: ff %d", c.ff);
       if (e->cfg.block == SSDK_BLOCK_SERIAL_POSTNORM) return fail("the ungated feed-forward is built for parallel blocks");
-      if (c.ff_act != SSDK_ACT_RELU2 && c.ff_act != SSDK_ACT_GELU_TANH && c.ff_act != SSDK_ACT_SILU) return fail("dense feed-forward: unknown activation %d", c.ff_act);
+      if (c.ff_act != SSDK_ACT_RELU2 && c.ff_act != SSDK_ACT_GELU_TANH && c.ff_act != SSDK_ACT_SILU && c.ff_act != SSDK_ACT_POLYNORM)
+        return fail("dense feed-forward: unknown activation %d", c.ff_act);
       up(e->w_sff2, c.ff); up(e->w_sff, c.ff);   // it shares the shared expert's buffers: no layer has both
       e->any_ffn = true;
     } else if (c.mlp == SSDK_MLP_MOE) {
@@ -189,9 +212,14 @@ static int hyb_derive(ssdk_hyb_engine* e) {
       if (c.keep < 1 || c.keep > c.groups) return fail("moe: keep %d of %d groups", c.keep, c.groups);
       if (c.top < 1 || c.top > 32 || c.top > c.keep * (Et / c.groups)) return fail("moe: top %d does not fit the kept groups", c.top);
       if (c.group_best != 1 && c.group_best != 2) return fail("moe: a group scores its 1 or 2 best, not %d", c.group_best);
-      if (c.expert_act != SSDK_ACT_CLAMPED && c.expert_act != SSDK_ACT_SILU) return fail("moe: unknown expert activation %d", c.expert_act);
-      up(e->w_e, Et); up(e->w_top, c.top); up(e->w_ff2, 2LL * c.ff); up(e->w_ff, c.ff);
-      if (c.shared_ff > 0) { up(e->w_sff2, 2LL * c.shared_ff + 1); up(e->w_sff, c.shared_ff); }
+      if (c.expert_glu) {
+        if (c.expert_act != SSDK_ACT_CLAMPED && c.expert_act != SSDK_ACT_SILU) return fail("moe: unknown gated expert activation %d", c.expert_act);
+      } else if (c.expert_act != SSDK_ACT_RELU2 && c.expert_act != SSDK_ACT_SILU && c.expert_act != SSDK_ACT_GELU_TANH) {
+        return fail("moe: unknown expert activation %d", c.expert_act);
+      }
+      const long long mats = c.expert_glu ? 2 : 1;   // stacked input matrices of an expert
+      up(e->w_e, Et); up(e->w_top, c.top); up(e->w_ff2, mats * c.ff); up(e->w_ff, c.ff);
+      if (c.shared_ff > 0) { up(e->w_sff2, mats * c.shared_ff + 1); up(e->w_sff, c.shared_ff); }
     } else if (c.mlp != SSDK_MLP_NONE) {
       return fail("hybrid layer: unknown feed-forward kind %d", c.mlp);
     }
@@ -209,7 +237,10 @@ static int64_t hyb_carve(ssdk_hyb_engine* e, uint8_t* base) {
   auto take = [&](size_t bytes) { uint8_t* p = base ? base + off : nullptr; off = align_up(off + bytes, 256); return p; };
   e->x = (float*)take(cap * g.width * 4);
   e->h = take(cap * g.width * es);
-  e->h2 = take(g.block == SSDK_BLOCK_PARALLEL_TWO_NORMS ? cap * g.width * es : 0);
+  const bool one_norm = g.block == SSDK_BLOCK_PARALLEL_ONE_NORM;
+  e->h2 = take(g.block == SSDK_BLOCK_PARALLEL_TWO_NORMS || (one_norm && g.canon_taps > 0) ? cap * g.width * es : 0);
+  e->hc = take(one_norm && g.canon_taps > 0 ? cap * g.width * es : 0);
+  e->gz = (float*)take(one_norm && g.gated_residual ? cap * 2 * g.width * 4 : 0);
   e->mixes = take(e->any_wkv ? 5 * cap * g.width * es : 0);
   e->p0 = (float*)take(cap * e->w_p0 * 4);
   e->p1 = (float*)take(cap * e->w_p1 * 4);
@@ -253,7 +284,7 @@ static int64_t hyb_carve(ssdk_hyb_engine* e, uint8_t* base) {
   e->meta = (int*)take(e->meta_ints * 4);
   // split-K partials of the tcgen05 GEMM: up to 8 splits of a 256-row call of the widest output, bounded at 64 MB
   size_t widest = std::max<size_t>(g.vocab, g.width);
-  for (int w : {e->w_p0, e->w_p1, e->w_sff2}) widest = std::max<size_t>(widest, (size_t)w);
+  for (int w : {e->w_p0, e->w_p1, e->w_sff2, one_norm ? 2 * g.width : 0}) widest = std::max<size_t>(widest, (size_t)w);
   e->partial_floats = es == 2 ? std::min<size_t>(8 * std::min<size_t>(cap, 256) * widest, 16u << 20) : 0;
   e->partials = (float*)take(e->partial_floats * 4);
   return (int64_t)off;
@@ -449,11 +480,14 @@ struct HybRun {
     return lin(e->t1, H * V, Lr.t[SSDK_HT_MIX_OUT].p, H * V, e->mix_out, W, M, W, H * V);
   }
 
+  // query rows per block of a windowed attention's portion path
+  static int window_block(int win) { return std::max(128, (win + 63) / 64 * 64); }
+
   int latent(HybLayer& Lr) {
     const ssdk_hyb_layer_cfg& c = Lr.c;
     const int H = c.heads, D = c.dim, V = c.vdim, R = c.rot_dim, KR = c.kv_rank, QR = c.q_rank, W = e->cfg.width;
     const bool own = c.kv_from < 0;   // the layer fills a pool of its own (else it reads an earlier layer's rows of this step and before)
-    const int Nq = H * (D + R), Nkv = own ? KR + R : 0;
+    const int Nq = H * (D + R), Nkv = own ? KR + R : 0, win = c.window;
     CKI(check_tensor(Lr, SSDK_HT_LAT_UKT, (int64_t)H * KR, D, "uk^T")); CKI(check_tensor(Lr, SSDK_HT_LAT_UV, (int64_t)H * V, KR, "uv"));
     CKI(check_tensor(Lr, SSDK_HT_MIX_OUT, W, (int64_t)H * V, "mix.o"));
     if (own) CKI(check_tensor(Lr, SSDK_HT_LAT_KVNORM, KR, 1, "dkv.norm"));
@@ -501,6 +535,7 @@ struct HybRun {
       int n_dec = 0, ctx_max = 0;
       for (int s = 0; s < rg.n_seqs; ++s)
         if (h_cu[s + 1] - h_cu[s] == 1) { ++n_dec; ctx_max = std::max(ctx_max, h_pos0[s] + 1); }
+      if (win > 0) ctx_max = std::min(ctx_max, win);
       const size_t smem = ssdk::latent_decode_smem(H, KR, Wd, sizeof(T));
       const bool pool_aligned = ((uintptr_t)pool & 15) == 0;
       // bf16 rows that start on 16-byte boundaries go through the tensor cores: k-steps of 16 columns and n-tiles of 8
@@ -515,7 +550,7 @@ struct HybRun {
         if (splits >= 1) {
           ssdk::LatentDecodeArgs da;
           da.qcat = e->qcat; da.cache = pool; da.sink = sink; da.part = e->att_s; da.out = e->t0;
-          da.H = H; da.KR = KR; da.W = Wd; da.splits = splits; da.scale = c.attn_scale; da.pool_aligned = pool_aligned;
+          da.H = H; da.KR = KR; da.W = Wd; da.splits = splits; da.scale = c.attn_scale; da.pool_aligned = pool_aligned; da.window = win;
           if (mma) {
             const dim3 grid(rg.n_seqs, splits, (H + 15) / 16), block(ssdk::kDmThreads);
             const size_t sm = ssdk::latent_decode_mma_smem(Wd);
@@ -535,25 +570,32 @@ struct HybRun {
     const bool tc_attn = !kF32 && e->use_tc && e->use_tc_scores;
     const int kpad = tc_attn ? 64 : 8;
     for (int s = 0; s < rg.n_seqs; ++s) {
-      const int r0 = h_cu[s], n = h_cu[s + 1] - r0, p0 = h_pos0[s], ctx = p0 + n, ctx_pad = (ctx + kpad - 1) / kpad * kpad;
+      const int r0 = h_cu[s], n = h_cu[s + 1] - r0, p0 = h_pos0[s];
       if (fused_decode && n == 1) continue;
-      CKI(L.go(ssdk::latent_gather_kernel<T>, dim3(ctx_pad), dim3(128), 0, (const T*)pool, (T*)e->keys, (T*)e->lat_t, rg, s, ctx, ctx_pad,
+      // the portion's keys: positions lo .. p0 + n - 1 (a window hides the positions before lo from every row of the portion)
+      const int lo = win > 0 ? std::max(0, p0 - win + 1) : 0, ctx = p0 + n - lo, ctx_pad = (ctx + kpad - 1) / kpad * kpad;
+      CKI(L.go(ssdk::latent_gather_kernel<T>, dim3(ctx_pad), dim3(128), 0, (const T*)pool, (T*)e->keys, (T*)e->lat_t, rg, s, lo, ctx, ctx_pad,
                KR, Wd));
-      const int qb = (int)std::max<size_t>(1, e->att_elems / ((size_t)H * ctx_pad));
+      int qb = (int)std::max<size_t>(1, e->att_elems / ((size_t)H * ctx_pad));
+      if (win > 0) qb = std::min(qb, window_block(win));   // short query blocks: a block's scores span its rows + the window
       for (int q0 = 0; q0 < n; q0 += qb) {
-        const int nq = std::min(qb, n - q0), rows = nq * H, cb = (p0 + q0 + nq + kpad - 1) / kpad * kpad;  // keys this block can see, padded
+        // gathered keys kb .. kb + cb - 1 are what this block can see (whole pads, so that the operands stay aligned)
+        const int nq = std::min(qb, n - q0), rows = nq * H, kb = win > 0 ? std::max(0, p0 + q0 - win + 1 - lo) / kpad * kpad : 0;
+        const int cb = (p0 + q0 + nq - lo - kb + kpad - 1) / kpad * kpad;
         const T* qrows = (const T*)e->qcat + (size_t)(r0 + q0) * H * Wd;
+        const T* krows = (const T*)e->keys + (size_t)kb * Wd;
+        const T* lat_t = (const T*)e->lat_t + kb;
         // scores: keys are the 128-row operand, (query, head) rows the tokens
-        CKI(lin(qrows, Wd, e->keys, Wd, e->att_s, cb, rows, cb, Wd, false, 1, 0, 0, 0, tc_attn));
+        CKI(lin(qrows, Wd, krows, Wd, e->att_s, cb, rows, cb, Wd, false, 1, 0, 0, 0, tc_attn));
         CKI(L.go(ssdk::sink_softmax_kernel<T>, dim3(rows), dim3(256), 0, (const float*)e->att_s, (T*)e->att_p,
-                 (const T*)sink, H, cb, p0 + q0, c.attn_scale, rows, 0.f));
+                 (const T*)sink, H, cb, p0 + q0, c.attn_scale, rows, 0.f, lo + kb, win));
         T* o_rows = (T*)e->t0 + (size_t)(r0 + q0) * H * KR;
-        if (tc_attn && tc_ok(e->att_p, cb, e->lat_t, ctx_pad, KR, KR, cb)) {
+        if (tc_attn && tc_ok(e->att_p, cb, lat_t, ctx_pad, KR, KR, cb)) {
           // P C: the transposed latents [kv_rank, ctx_pad] are the 128-row operand, read with the row stride of the gather
-          CKI(lin_tc(e->att_p, e->lat_t, e->att_o, rows, KR, cb, ctx_pad));
+          CKI(lin_tc(e->att_p, lat_t, e->att_o, rows, KR, cb, ctx_pad));
           CKI(L.go(ssdk::cast_cols_kernel<T>, dim3(rows), dim3(128), 0, (const float*)e->att_o, KR, o_rows, KR, KR));
         } else {
-          CKI(lin(e->att_p, cb, e->lat_t, ctx_pad, o_rows, KR, rows, KR, cb, true, 1, 0, 0, 0, false));
+          CKI(lin(e->att_p, cb, lat_t, ctx_pad, o_rows, KR, rows, KR, cb, true, 1, 0, 0, 0, false));
         }
       }
     }
@@ -570,16 +612,29 @@ struct HybRun {
 
   const void* fin = nullptr;   // the feed-forward's input in the storage type (the mixer's input, or the second norm's rows)
 
+  // an expert's activation over `rows` rows of z [rows, ldz] -> y [rows, ff]: gated (z = gate | up columns) or not (z = up columns)
+  int expert_act(const ssdk_hyb_layer_cfg& c, const float* z, int ldz, T* y, int ff, float limit, int rows, const int* n_rows) {
+    const dim3 grid(rows), block(128);
+    if (c.expert_glu) {
+      if (c.expert_act == SSDK_ACT_SILU) return L.go(ssdk::glu_act_kernel<T, SSDK_ACT_SILU>, grid, block, 0, z, ldz, y, ff, n_rows);
+      return L.go(ssdk::clamped_glu_kernel<T>, grid, block, 0, z, ldz, y, ff, limit, n_rows);
+    }
+    if (c.expert_act == SSDK_ACT_SILU) return L.go(ssdk::act_cols_kernel<T, SSDK_ACT_SILU>, grid, block, 0, z, ldz, y, ff, n_rows);
+    if (c.expert_act == SSDK_ACT_GELU_TANH) return L.go(ssdk::act_cols_kernel<T, SSDK_ACT_GELU_TANH>, grid, block, 0, z, ldz, y, ff, n_rows);
+    return L.go(ssdk::act_cols_kernel<T, SSDK_ACT_RELU2>, grid, block, 0, z, ldz, y, ff, n_rows);
+  }
+
   int moe(HybLayer& Lr) {
     const ssdk_hyb_layer_cfg& c = Lr.c;
     const int W = e->cfg.width, E = c.experts, Et = E + c.identity, ff = c.ff, top = c.top, A = M * top;
-    CKI(check_tensor(Lr, SSDK_HT_ROUTER, Et, W, "router")); CKI(check_tensor(Lr, SSDK_HT_EXPERT_IN, (int64_t)E * 2 * ff, W, "experts.in"));
+    const int Nin = c.expert_glu ? 2 * ff : ff;   // rows of an expert's stacked input matrices
+    CKI(check_tensor(Lr, SSDK_HT_ROUTER, Et, W, "router")); CKI(check_tensor(Lr, SSDK_HT_EXPERT_IN, (int64_t)E * Nin, W, "experts.in"));
     CKI(check_tensor(Lr, SSDK_HT_EXPERT_OUT, (int64_t)E * W, ff, "experts.out"));
     if (c.route_bias) CKI(check_tensor(Lr, SSDK_HT_ROUTER_BIAS, Et, 1, "router.bias"));
     CKI(lin(fin, W, Lr.t[SSDK_HT_ROUTER].p, W, e->rz, Et, M, Et, W));
     ssdk::RouterArgs ra;
     ra.z = e->rz; ra.bias = c.route_bias ? Lr.t[SSDK_HT_ROUTER_BIAS].p : nullptr; ra.sel = e->sel; ra.wts = e->wts; ra.M = M; ra.E = Et;
-    ra.top = top; ra.groups = c.groups; ra.keep = c.keep; ra.softmax = c.route_softmax; ra.group_best = c.group_best;
+    ra.top = top; ra.groups = c.groups; ra.keep = c.keep; ra.softmax = c.route_top_softmax ? 2 : c.route_softmax; ra.group_best = c.group_best;
     ra.renorm = c.route_renorm; ra.route_scale = c.route_scale;
     CKI(L.go(ssdk::group_topk_router_kernel<T>, dim3((M + ssdk::kRouterWarps - 1) / ssdk::kRouterWarps), dim3(ssdk::kRouterWarps * 32), 0, ra));
     // many rows in bf16 with whole k-blocks: the grouped tcgen05 GEMM over rows gathered per expert (tiles of 128 rows);
@@ -596,17 +651,14 @@ struct HybRun {
     ssdk::LinearArgs a = {};
     if (tc_moe) {
       CKI(L.go(ssdk::gather_rows_kernel<T>, dim3(A), dim3(128), 0, (const T*)fin, (const int*)e->arow, (const int*)e->n_rows, (T*)e->xs, W));
-      CKI(lin_tc_grouped(e->xs, Lr.t[SSDK_HT_EXPERT_IN].p, e->eg, A, 2 * ff, W, E, tile, A / tile + E + 1));
+      CKI(lin_tc_grouped(e->xs, Lr.t[SSDK_HT_EXPERT_IN].p, e->eg, A, Nin, W, E, tile, A / tile + E + 1));
     } else {
-      a.A = fin; a.W = Lr.t[SSDK_HT_EXPERT_IN].p; a.C = e->eg; a.M = A; a.N = 2 * ff; a.K = W; a.lda = W; a.ldw = W; a.ldc = 2 * ff;
+      a.A = fin; a.W = Lr.t[SSDK_HT_EXPERT_IN].p; a.C = e->eg; a.M = A; a.N = Nin; a.K = W; a.lda = W; a.ldw = W; a.ldc = Nin;
       a.a_rows = e->arow; a.tile_expert = e->tile_expert; a.tile_row0 = e->tile_row0; a.tile_rows = e->tile_rows; a.n_tiles = e->n_tiles;
-      a.sW_expert = (long long)2 * ff * W;
+      a.sW_expert = (long long)Nin * W;
       CKI(lin_args<float>(a, A, 1));
     }
-    if (c.expert_act == SSDK_ACT_SILU)
-      CKI(L.go(ssdk::glu_act_kernel<T, SSDK_ACT_SILU>, dim3(A), dim3(128), 0, (const float*)e->eg, 2 * ff, (T*)e->ey, ff, n_real_rows));
-    else
-      CKI(L.go(ssdk::clamped_glu_kernel<T>, dim3(A), dim3(128), 0, (const float*)e->eg, 2 * ff, (T*)e->ey, ff, c.limit, n_real_rows));
+    CKI(expert_act(c, (const float*)e->eg, Nin, (T*)e->ey, ff, c.limit, A, n_real_rows));
     if (tc_moe) {
       CKI(lin_tc_grouped(e->ey, Lr.t[SSDK_HT_EXPERT_OUT].p, e->eo, A, W, ff, E, tile, A / tile + E + 1));
     } else {
@@ -616,13 +668,10 @@ struct HybRun {
       CKI(lin_args<float>(a, A, 1));
     }
     if (c.shared_ff > 0) {
-      const int sff = c.shared_ff, Ns = 2 * sff + (c.shared_gate ? 1 : 0);
+      const int sff = c.shared_ff, Ns = (c.expert_glu ? 2 : 1) * sff + (c.shared_gate ? 1 : 0);
       CKI(check_tensor(Lr, SSDK_HT_SHARED_IN, Ns, W, "shared.in")); CKI(check_tensor(Lr, SSDK_HT_SHARED_OUT, W, sff, "shared.out"));
       CKI(lin(fin, W, Lr.t[SSDK_HT_SHARED_IN].p, W, e->sz, Ns, M, Ns, W));
-      if (c.expert_act == SSDK_ACT_SILU)
-        CKI(L.go(ssdk::glu_act_kernel<T, SSDK_ACT_SILU>, dim3(M), dim3(128), 0, (const float*)e->sz, Ns, (T*)e->sy, sff, (const int*)nullptr));
-      else
-        CKI(L.go(ssdk::clamped_glu_kernel<T>, dim3(M), dim3(128), 0, (const float*)e->sz, Ns, (T*)e->sy, sff, c.shared_limit, (const int*)nullptr));
+      CKI(expert_act(c, (const float*)e->sz, Ns, (T*)e->sy, sff, c.shared_limit, M, (const int*)nullptr));
       CKI(lin(e->sy, sff, Lr.t[SSDK_HT_SHARED_OUT].p, sff, e->so, W, M, W, sff));
     }
     return 0;
@@ -637,7 +686,11 @@ struct HybRun {
     if (Lr.t[SSDK_HT_FFN_OUT_B].p) CKI(check_tensor(Lr, SSDK_HT_FFN_OUT_B, W, 1, "mlp.down.b"));
     CKI(lin(fin, W, Lr.t[SSDK_HT_FFN_IN].p, W, e->sz, ff, M, ff, W));
     const dim3 grid(M), block(256);
-    if (Lr.c.ff_act == SSDK_ACT_RELU2) CKI(L.go(ssdk::bias_act_kernel<T, SSDK_ACT_RELU2>, grid, block, 0, (const float*)e->sz, b_up, (T*)e->sy, ff));
+    if (Lr.c.ff_act == SSDK_ACT_POLYNORM) {
+      if (b_up) return fail("the PolyNorm feed-forward has no input bias");
+      CKI(check_tensor(Lr, SSDK_HT_FFN_ACT, 4, 1, "mlp.act"));
+      CKI(L.go(ssdk::polynorm_kernel<T>, grid, block, 0, (const float*)e->sz, (const T*)Lr.t[SSDK_HT_FFN_ACT].p, (T*)e->sy, ff, e->cfg.eps));
+    } else if (Lr.c.ff_act == SSDK_ACT_RELU2) CKI(L.go(ssdk::bias_act_kernel<T, SSDK_ACT_RELU2>, grid, block, 0, (const float*)e->sz, b_up, (T*)e->sy, ff));
     else if (Lr.c.ff_act == SSDK_ACT_SILU) CKI(L.go(ssdk::bias_act_kernel<T, SSDK_ACT_SILU>, grid, block, 0, (const float*)e->sz, b_up, (T*)e->sy, ff));
     else CKI(L.go(ssdk::bias_act_kernel<T, SSDK_ACT_GELU_TANH>, grid, block, 0, (const float*)e->sz, b_up, (T*)e->sy, ff));
     return lin(e->sy, ff, Lr.t[SSDK_HT_FFN_OUT].p, ff, e->so, W, M, W, ff);
@@ -735,20 +788,23 @@ struct HybRun {
   }
 
   // grouped-query sink attention over the layer's page pool: z holds q | k | v (fp32); og [G, M, H/G, V] fp32
-  int gqa_attention(HybLayer& Lr, const float* z, int ldz, float* og) {
+  int gqa_attention(HybLayer& Lr, const float* z, int ldz, float* og, const void* sinks = nullptr) {
     const ssdk_hyb_layer_cfg& c = Lr.c;
-    const int H = c.heads, G = c.kv_heads, D = c.dim, V = c.vdim, hpg = H / G;
+    const int H = c.heads, G = c.kv_heads, D = c.dim, V = c.vdim, hpg = H / G, win = c.window;
+    const float sink_const = sinks ? 0.f : c.sink;
     if (!e->cache) return fail("hybrid: attention cache not bound");
     uint8_t* pool = e->cache + (size_t)e->num_blocks * e->cfg.block_size * Lr.cache_rows_before * e->esz;
     ssdk::GqaPrepArgs pa;
     pa.z = z; pa.ldz = ldz; pa.q = e->qcat; pa.cache = pool; pa.inv_freq = c.rot_dims >= 2 ? Lr.inv_freq : nullptr;
     pa.H = H; pa.G = G; pa.D = D; pa.V = V; pa.rot_dims = c.rot_dims; pa.qk_norm = c.qk_norm; pa.rot_mult = Lr.rot_mult; pa.eps = e->cfg.eps;
+    pa.rot_half = c.rot_half;
     CKI(L.go(ssdk::gqa_prep_kernel<T>, dim3(M, H + G), dim3(32), 0, pa, rg));
     bool fused_decode = false;
     {
       int n_dec = 0, ctx_max = 0;
       for (int s = 0; s < rg.n_seqs; ++s)
         if (h_cu[s + 1] - h_cu[s] == 1) { ++n_dec; ctx_max = std::max(ctx_max, h_pos0[s] + 1); }
+      if (win > 0) ctx_max = std::min(ctx_max, win);
       const int vpl = (V + 31) / 32;
       if (n_dec > 0 && vpl <= 8 && e->use_decode_attn) {
         int splits = std::max(1, std::min({32, 8 * num_sms() / std::max(1, n_dec * H), (ctx_max + 127) / 128}));  // ~8 four-warp CTAs per SM
@@ -757,35 +813,58 @@ struct HybRun {
         if (splits >= 1) {
           ssdk::GqaDecodeArgs da;
           da.q = e->qcat; da.cache = pool; da.part = e->att_s; da.out = og; da.H = H; da.G = G; da.D = D; da.V = V; da.splits = splits;
-          da.scale = c.attn_scale; da.sink = c.sink;
+          da.scale = c.attn_scale; da.sink = sink_const; da.sinks = sinks; da.window = win;
           const dim3 grid(rg.n_seqs, H, splits), block(ssdk::kGqaDecWarps * 32);
           const size_t smem = ssdk::gqa_decode_smem(D, V);
           if (vpl <= 1) CKI(L.go(ssdk::gqa_decode_partial_kernel<T, 1>, grid, block, smem, da, rg));
           else if (vpl <= 2) CKI(L.go(ssdk::gqa_decode_partial_kernel<T, 2>, grid, block, smem, da, rg));
           else if (vpl <= 4) CKI(L.go(ssdk::gqa_decode_partial_kernel<T, 4>, grid, block, smem, da, rg));
           else CKI(L.go(ssdk::gqa_decode_partial_kernel<T, 8>, grid, block, smem, da, rg));
-          CKI(L.go(ssdk::gqa_decode_merge_kernel, dim3(rg.n_seqs, H), dim3(64), 0, da, rg));
+          CKI(L.go(ssdk::gqa_decode_merge_kernel<T>, dim3(rg.n_seqs, H), dim3(64), 0, da, rg));
           fused_decode = true;
         }
       }
     }
     for (int s = 0; s < rg.n_seqs; ++s) {
-      const int r0 = h_cu[s], n = h_cu[s + 1] - r0, p0 = h_pos0[s], ctx = p0 + n, ctx_pad = (ctx + 7) / 8 * 8;
+      const int r0 = h_cu[s], n = h_cu[s + 1] - r0, p0 = h_pos0[s];
       if (fused_decode && n == 1) continue;
-      CKI(L.go(ssdk::kv_gather_kernel<T>, dim3(ctx_pad), dim3(128), 0, (const T*)pool, (T*)e->keys, (T*)e->lat_t, rg, s, ctx, ctx_pad, G, D, V));
-      const int qb = (int)std::max<size_t>(1, e->att_elems / ((size_t)H * ctx_pad));
+      const int lo = win > 0 ? std::max(0, p0 - win + 1) : 0, ctx = p0 + n - lo, ctx_pad = (ctx + 7) / 8 * 8;   // keys lo .. p0 + n - 1
+      CKI(L.go(ssdk::kv_gather_kernel<T>, dim3(ctx_pad), dim3(128), 0, (const T*)pool, (T*)e->keys, (T*)e->lat_t, rg, s, lo, ctx, ctx_pad, G, D, V));
+      int qb = (int)std::max<size_t>(1, e->att_elems / ((size_t)H * ctx_pad));
+      if (win > 0) qb = std::min(qb, window_block(win));
       for (int q0 = 0; q0 < n; q0 += qb) {
-        const int nq = std::min(qb, n - q0), rows = nq * hpg, cb = (p0 + q0 + nq + 7) / 8 * 8;
+        const int nq = std::min(qb, n - q0), rows = nq * hpg, kb = win > 0 ? std::max(0, p0 + q0 - win + 1 - lo) / 8 * 8 : 0;
+        const int cb = (p0 + q0 + nq - lo - kb + 7) / 8 * 8;   // gathered keys kb .. kb + cb - 1 are what this block can see
         const T* qrows = (const T*)e->qcat + (size_t)(r0 + q0) * hpg * D;
-        CKI(lin(qrows, D, e->keys, D, e->att_s, cb, rows, cb, D, false, G, (long long)M * hpg * D, (long long)ctx_pad * D,
+        CKI(lin(qrows, D, (const T*)e->keys + (size_t)kb * D, D, e->att_s, cb, rows, cb, D, false, G, (long long)M * hpg * D, (long long)ctx_pad * D,
                 (long long)rows * cb, false));
-        CKI(L.go(ssdk::sink_softmax_kernel<T>, dim3(G * rows), dim3(256), 0, (const float*)e->att_s, (T*)e->att_p, (const T*)nullptr, hpg, cb,
-                 p0 + q0, c.attn_scale, rows, c.sink));
-        CKI(lin(e->att_p, cb, e->lat_t, ctx_pad, og + (size_t)(r0 + q0) * hpg * V, V, rows, V, cb, false, G, (long long)rows * cb,
+        CKI(L.go(ssdk::sink_softmax_kernel<T>, dim3(G * rows), dim3(256), 0, (const float*)e->att_s, (T*)e->att_p, (const T*)sinks, hpg, cb,
+                 p0 + q0, c.attn_scale, rows, sink_const, lo + kb, win));
+        CKI(lin(e->att_p, cb, (const T*)e->lat_t + kb, ctx_pad, og + (size_t)(r0 + q0) * hpg * V, V, rows, V, cb, false, G, (long long)rows * cb,
                 (long long)V * ctx_pad, (long long)M * hpg * V, false));
       }
     }
     return 0;
+  }
+
+  // grouped-query attention alone: stacked q | k | v projection, its bias, a short convolution over time on every channel
+  // (history in the state slot), rotation, window, learned sink, output projection
+  int attention(HybLayer& Lr) {
+    const ssdk_hyb_layer_cfg& c = Lr.c;
+    const int W = e->cfg.width, H = c.heads, G = c.kv_heads, D = c.dim, V = c.vdim, taps = c.conv, Nqkv = H * D + G * D + G * V;
+    CKI(check_tensor(Lr, SSDK_HT_ATTN_IN, Nqkv, W, "attention.in")); CKI(check_tensor(Lr, SSDK_HT_CONV_W, Nqkv, taps, "attention.conv"));
+    CKI(check_tensor(Lr, SSDK_HT_MIX_OUT, W, (int64_t)H * V, "mix.o"));
+    if (Lr.t[SSDK_HT_ATTN_IN_B].p) CKI(check_tensor(Lr, SSDK_HT_ATTN_IN_B, Nqkv, 1, "attention.in.b"));
+    if (c.learned_sink) CKI(check_tensor(Lr, SSDK_HT_ATTN_SINK, H, 1, "sink"));
+    CKI(lin(hin, W, Lr.t[SSDK_HT_ATTN_IN].p, W, e->p0, Nqkv, M, Nqkv, W));
+    ssdk::ConvArgs ca = {};
+    ca.in = e->p0; ca.ld_in = Nqkv; ca.in_bias = Lr.t[SSDK_HT_ATTN_IN_B].p; ca.w = Lr.t[SSDK_HT_CONV_W].p; ca.out = e->p1; ca.ld_out = Nqkv;
+    ca.hist = e->state + Lr.state_off; ca.slot_stride = e->slot_floats; ca.C = Nqkv; ca.taps = taps;
+    CKI(L.go(ssdk::short_conv_kernel<T, 0>, dim3(M, (Nqkv + 255) / 256), dim3(256), 0, ca, rg));
+    if (taps > 1) CKI(L.go(ssdk::conv_state_kernel<T>, dim3(rg.n_seqs, (Nqkv + 255) / 256), dim3(256), 0, ca, rg));
+    CKI(gqa_attention(Lr, e->p1, Nqkv, e->p2, c.learned_sink ? Lr.t[SSDK_HT_ATTN_SINK].p : nullptr));
+    CKI(L.go(ssdk::attn_gate_kernel<T>, dim3(M), dim3(256), 0, (const float*)e->p2, (const float*)nullptr, 0, (T*)e->t0, M, H, G, V));
+    return lin(e->t0, H * V, Lr.t[SSDK_HT_MIX_OUT].p, H * V, e->mix_out, W, M, W, H * V);
   }
 
   int attn_delta(HybLayer& Lr) {
@@ -843,6 +922,7 @@ struct HybRun {
       case SSDK_MIX_LATENT_ATTN: return latent(Lr);
       case SSDK_MIX_RGLRU: return rglru(Lr);
       case SSDK_MIX_SELECTIVE: return selective(Lr);
+      case SSDK_MIX_ATTENTION: return attention(Lr);
       default: return attn_delta(Lr);
     }
   }
@@ -874,27 +954,52 @@ struct HybRun {
     if (e->cfg.block == SSDK_BLOCK_SERIAL_POSTNORM) return serial_layer(Lr);
     const int W = e->cfg.width;
     const bool two = e->cfg.block == SSDK_BLOCK_PARALLEL_TWO_NORMS;   // norm1 feeds the mixer, norm2 the feed-forward; no layer scales
+    const bool one = e->cfg.block == SSDK_BLOCK_PARALLEL_ONE_NORM;    // one norm; input convolutions and residual gates; no layer scales
+    const bool scales = !two && !one;
     const bool ff2 = two && Lr.c.mlp != SSDK_MLP_NONE;
     hin = e->h;
     fin = ff2 ? e->h2 : e->h;
     CKI(check_tensor(Lr, SSDK_HT_NORM, W, 1, "norm1"));
-    if (!two) CKI(check_tensor(Lr, SSDK_HT_LS_MIX, W, 1, "ls1"));
+    if (scales) CKI(check_tensor(Lr, SSDK_HT_LS_MIX, W, 1, "ls1"));
     if (ff2) CKI(check_tensor(Lr, SSDK_HT_NORM2, W, 1, "norm2"));
     CKI(L.go(ssdk::offset_rmsnorm_kernel<T>, dim3(M), dim3(256), 0, (const float*)e->x, (const T*)Lr.t[SSDK_HT_NORM].p, (T*)e->h,
              (const int*)nullptr, W, e->cfg.eps, e->cfg.norm_offset, ff2 ? (const T*)Lr.t[SSDK_HT_NORM2].p : (const T*)nullptr,
              ff2 ? (T*)e->h2 : (T*)nullptr));
-    if (Lr.c.mixer == SSDK_MIX_ATTN_DELTA) return fail("the attention pair is built for serial blocks");
-    CKI(run_mixer(Lr));
     ssdk::CombineArgs ca = {};
-    ca.x = e->x; ca.mix = e->mix_out; ca.ls1 = two ? nullptr : Lr.t[SSDK_HT_LS_MIX].p; ca.width = W;
+    if (one) {
+      const bool has_ff = Lr.c.mlp != SSDK_MLP_NONE;
+      const int taps = e->cfg.canon_taps, sub = has_ff ? 2 : 1;   // sublayers that have an input convolution and a gate
+      if (taps > 0) {
+        // each sublayer reads h + conv(h) with its own taps; the last taps - 1 rows of h live in the state slot
+        CKI(check_tensor(Lr, SSDK_HT_CANON_W, (int64_t)sub * W, taps, "canon"));
+        ssdk::InputConvArgs ia;
+        ia.h = e->h; ia.w = Lr.t[SSDK_HT_CANON_W].p; ia.y1 = e->hc; ia.y2 = has_ff ? e->h2 : nullptr;
+        ia.hist = e->state + Lr.canon_off; ia.slot_stride = e->slot_floats; ia.C = W; ia.taps = taps;
+        CKI(L.go(ssdk::input_conv_kernel<T>, dim3(M, (W + 255) / 256), dim3(256), 0, ia, rg));
+        if (taps > 1) CKI(L.go(ssdk::input_conv_state_kernel<T>, dim3(rg.n_seqs, (W + 255) / 256), dim3(256), 0, ia, rg));
+        hin = e->hc;
+        fin = e->h2;
+      }
+      if (e->cfg.gated_residual) {
+        // the gates read the normed rows themselves (before the input convolutions): one stacked product for both sublayers
+        CKI(check_tensor(Lr, SSDK_HT_RES_GATE, (int64_t)sub * W, W, "residual gates")); CKI(check_tensor(Lr, SSDK_HT_RES_GATE_B, (int64_t)sub * W, 1, "residual gates' bias"));
+        CKI(lin(e->h, W, Lr.t[SSDK_HT_RES_GATE].p, W, e->gz, sub * W, M, sub * W, W));
+        ca.gz = e->gz; ca.ld_gz = sub * W; ca.gz_bias = Lr.t[SSDK_HT_RES_GATE_B].p;
+      }
+    }
+    if (Lr.c.mixer == SSDK_MIX_ATTN_DELTA) return fail("the attention pair is built for serial blocks");
+    if (Lr.c.mixer == SSDK_MIX_ATTENTION && !one) return fail("the attention mixer is built for one-norm blocks");
+    CKI(run_mixer(Lr));
+    ca.x = e->x; ca.mix = e->mix_out; ca.ls1 = scales ? Lr.t[SSDK_HT_LS_MIX].p : nullptr; ca.width = W;
     if (Lr.c.mlp == SSDK_MLP_MOE) {
-      if (!two) CKI(check_tensor(Lr, SSDK_HT_LS_MLP, W, 1, "ls2"));
+      if (scales) CKI(check_tensor(Lr, SSDK_HT_LS_MLP, W, 1, "ls2"));
       CKI(moe(Lr));
-      ca.ls2 = two ? nullptr : Lr.t[SSDK_HT_LS_MLP].p; ca.routed = e->eo; ca.apos = e->apos; ca.wts = e->wts; ca.top = Lr.c.top;
+      ca.ls2 = scales ? Lr.t[SSDK_HT_LS_MLP].p : nullptr; ca.routed = e->eo; ca.apos = e->apos; ca.wts = e->wts; ca.top = Lr.c.top;
       if (Lr.c.identity > 0) { ca.sel = e->sel; ca.n_real = Lr.c.experts; ca.fin = fin; }
       if (Lr.c.shared_ff > 0) {
         ca.shared = e->so;
-        if (Lr.c.shared_gate) { ca.sg = e->sz + 2 * Lr.c.shared_ff; ca.ld_sg = 2 * Lr.c.shared_ff + 1; }
+        const int ld = (Lr.c.expert_glu ? 2 : 1) * Lr.c.shared_ff;
+        if (Lr.c.shared_gate) { ca.sg = e->sz + ld; ca.ld_sg = ld + 1; }
       }
     } else if (Lr.c.mlp == SSDK_MLP_FFN) {
       CKI(ffn(Lr));
@@ -1002,7 +1107,10 @@ int ssdk_hyb_create(const ssdk_hyb_cfg* cfg, const ssdk_hyb_layer_cfg* layers, s
   if (!cfg || !layers || !out) return fail("ssdk_hyb_create: null argument");
   if (cfg->width < 1 || cfg->vocab < 1 || cfg->n_layers < 1) return fail("ssdk_hyb_create: bad sizes");
   if (cfg->dtype != SSDK_DT_F32 && cfg->dtype != SSDK_DT_BF16) return fail("ssdk_hyb_create: unknown dtype %d", cfg->dtype);
-  if (cfg->block != SSDK_BLOCK_PARALLEL_PRENORM && cfg->block != SSDK_BLOCK_SERIAL_POSTNORM && cfg->block != SSDK_BLOCK_PARALLEL_TWO_NORMS) return fail("ssdk_hyb_create: unknown block kind %d", cfg->block);
+  if (cfg->block != SSDK_BLOCK_PARALLEL_PRENORM && cfg->block != SSDK_BLOCK_SERIAL_POSTNORM && cfg->block != SSDK_BLOCK_PARALLEL_TWO_NORMS &&
+      cfg->block != SSDK_BLOCK_PARALLEL_ONE_NORM) return fail("ssdk_hyb_create: unknown block kind %d", cfg->block);
+  if (cfg->canon_taps < 0 || (cfg->block != SSDK_BLOCK_PARALLEL_ONE_NORM && (cfg->canon_taps || cfg->gated_residual)))
+    return fail("ssdk_hyb_create: input convolutions and residual gates belong to one-norm blocks");
   if (cfg->max_tokens < 1 || cfg->max_seqs < 1 || cfg->max_logit_rows < 1 || cfg->block_size < 1 || cfg->max_blocks_per_seq < 1)
     return fail("ssdk_hyb_create: bad runtime limits");
   int ndev = 0;
@@ -1019,7 +1127,7 @@ int ssdk_hyb_create(const ssdk_hyb_cfg* cfg, const ssdk_hyb_layer_cfg* layers, s
   for (int i = 0; i < cfg->n_layers; ++i) e->layers[i].c = layers[i];
   if (hyb_derive(e) != 0) { delete e; return -1; }
   for (auto& L : e->layers) {
-    if ((L.c.mixer != SSDK_MIX_LATENT_ATTN && L.c.mixer != SSDK_MIX_ATTN_DELTA) || L.c.rot_dims < 2) continue;
+    if ((L.c.mixer != SSDK_MIX_LATENT_ATTN && L.c.mixer != SSDK_MIX_ATTN_DELTA && L.c.mixer != SSDK_MIX_ATTENTION) || L.c.rot_dims < 2) continue;
     const int half = L.c.rot_dims / 2;
     std::vector<float> f(half);
     const double dims = (double)L.c.rot_dims, base = (double)L.c.rot_base;

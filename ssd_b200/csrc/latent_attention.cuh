@@ -96,13 +96,14 @@ __global__ void latent_q_kernel(const float* __restrict__ q, int ldq, T* __restr
     st_f<T>(qcat + ((size_t)m * H + hd) * (KR + R) + KR + c, rope_entry(zr, c, rot_dims, interleaved, pos, inv_freq));
 }
 
-// One sequence's cached rows, made contiguous for the two attention GEMMs: keys [ctx_pad, W] (W = kv_rank + R) and the
-// latents transposed, lat_t [kv_rank, ctx_pad]; rows / columns from ctx up to ctx_pad (a multiple of 8) are zero.
+// One sequence's cached rows of positions lo .. lo + ctx - 1, made contiguous for the two attention GEMMs: keys [ctx_pad, W]
+// (W = kv_rank + R) and the latents transposed, lat_t [kv_rank, ctx_pad]; rows / columns from ctx up to ctx_pad (a multiple
+// of 8) are zero.  lo > 0 when a sliding window hides the sequence's first positions from the whole portion.
 template <typename T>
 __global__ void latent_gather_kernel(const T* __restrict__ cache, T* __restrict__ keys, T* __restrict__ lat_t, const Ragged rg,
-                                     int s, int ctx, int ctx_pad, int KR, int W) {
+                                     int s, int lo, int ctx, int ctx_pad, int KR, int W) {
   const int j = blockIdx.x;
-  const T* row = j < ctx ? cache + page_row(rg, s, j) * (size_t)W : nullptr;
+  const T* row = j < ctx ? cache + page_row(rg, s, lo + j) * (size_t)W : nullptr;
   for (int d = threadIdx.x; d < W; d += blockDim.x) {
     const float v = row ? ld_f<T>(row + d) : 0.f;
     st_f<T>(keys + (size_t)j * W + d, v);
@@ -112,20 +113,23 @@ __global__ void latent_gather_kernel(const T* __restrict__ cache, T* __restrict_
 
 // Softmax with a sink over the score rows of one query block.  The rows come in `batches` of rows_per_batch (one batch
 // per key/value head of grouped-query attention; a single batch for latent attention); inside a batch row r is
-// (query q0 + r / H, head r % H) with H the heads that share the batch's keys, and the query at position pos sees keys
-// 0 .. pos.  sc [rows, ld] fp32 raw dot products -> pr [rows, ld] (T) weights, zero beyond pos and in the padding.
+// (query q0 + r / H, head r % H) with H the heads that share the batch's keys.  Column j of a row is the key at position
+// key_first + j; the query at position pos sees the keys at max(0, pos - window + 1) .. pos (window = 0: at 0 .. pos).
+// sc [rows, ld] fp32 raw dot products -> pr [rows, ld] (T) weights, zero outside the visible range and in the padding.
 // The sink is a learned per-head logit (`sink`, indexed batch * H + head) or, without one, the constant sink_const added
 // to the denominator (0: plain softmax); it joins the maximum, is not scaled and contributes nothing to the output.
 template <typename T>
 __global__ void sink_softmax_kernel(const float* __restrict__ sc, T* __restrict__ pr, const T* __restrict__ sink, int H, int ld,
-                                    int pos_first, float scale, int rows_per_batch, float sink_const) {
+                                    int pos_first, float scale, int rows_per_batch, float sink_const, int key_first, int window) {
   __shared__ float red[33];
   const int r = blockIdx.x, batch = r / rows_per_batch, rb = r - batch * rows_per_batch;
-  const int h = rb % H, n = pos_first + rb / H + 1;  // keys this row sees
+  const int h = rb % H, pos = pos_first + rb / H;
+  const int n = pos - key_first + 1;                                             // columns [j0, n) are the keys this row sees
+  const int j0 = window > 0 ? max(0, pos - window + 1 - key_first) : 0;
   const float* srow = sc + (size_t)r * ld;
   const float sk = sink ? ld_f<T>(sink + batch * H + h) : (sink_const > 0.f ? logf(sink_const) : -INFINITY);
   float mx = sk;
-  for (int j = threadIdx.x; j < n; j += blockDim.x) mx = fmaxf(mx, srow[j] * scale);
+  for (int j = j0 + threadIdx.x; j < n; j += blockDim.x) mx = fmaxf(mx, srow[j] * scale);
   __syncthreads();
   mx = warp_max(mx);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
@@ -133,10 +137,11 @@ __global__ void sink_softmax_kernel(const float* __restrict__ sc, T* __restrict_
   mx = red[0];
   for (int w = 1; w < (int)(blockDim.x >> 5); ++w) mx = fmaxf(mx, red[w]);
   float sum = 0.f;
-  for (int j = threadIdx.x; j < n; j += blockDim.x) sum += expf(srow[j] * scale - mx);
+  for (int j = j0 + threadIdx.x; j < n; j += blockDim.x) sum += expf(srow[j] * scale - mx);
   sum = block_sum(sum, red) + expf(sk - mx);
   const float inv = 1.0f / sum;
-  for (int j = threadIdx.x; j < ld; j += blockDim.x) st_f<T>(pr + (size_t)r * ld + j, j < n ? expf(srow[j] * scale - mx) * inv : 0.f);
+  for (int j = threadIdx.x; j < ld; j += blockDim.x)
+    st_f<T>(pr + (size_t)r * ld + j, (j >= j0 && j < n) ? expf(srow[j] * scale - mx) * inv : 0.f);
 }
 
 // ---- single-token (decode) rows: one launch over all such sequences, the context split flash-decoding style ----
@@ -149,7 +154,15 @@ struct LatentDecodeArgs {
   int H, KR, W, splits;
   int pool_aligned;   // the pool starts on a 16-byte boundary
   float scale;
+  int window;         // the token at position p sees the keys at max(0, p - window + 1) .. p; 0: all of 0 .. p
 };
+
+// keys [k_lo, k_hi) of split j (of `splits`) for a single token at position ctx - 1
+SSDK_DEVINL void decode_split(int ctx, int window, int j, int splits, int* k_lo, int* k_hi) {
+  const int first = window > 0 ? max(0, ctx - window) : 0, per = (ctx - first + splits - 1) / splits;
+  *k_lo = first + j * per;
+  *k_hi = min(ctx, *k_lo + per);
+}
 
 constexpr int kDecTile = 16, kDecThreads = 256;
 
@@ -182,8 +195,8 @@ __global__ void __launch_bounds__(kDecThreads) latent_decode_partial_kernel(cons
   float* rs = ls + H;                      // [H] rescale of this tile
   T* ct = (T*)(rs + H);                    // [kDecTile, W] key rows
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int ctx = rg.pos0[s] + 1, per = (ctx + p.splits - 1) / p.splits;
-  const int k_lo = j * per, k_hi = min(ctx, k_lo + per);
+  int k_lo, k_hi;
+  decode_split(rg.pos0[s] + 1, p.window, j, p.splits, &k_lo, &k_hi);
   const T* q = (const T*)p.qcat + (size_t)row * H * W;
   constexpr int kPerVec = 16 / (int)sizeof(T);
   const size_t ct_off = ((size_t)kDecTile * Hp + (size_t)H * W + (size_t)H * KR + 3 * (size_t)H) * 4;
@@ -312,8 +325,8 @@ __global__ void __launch_bounds__(kDmThreads) latent_decode_mma_kernel(const Lat
   float* ls = mx + 16;                                         // [16] running sum
   float* rs = ls + 16;                                         // [16] rescale of this tile
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
-  const int ctx = rg.pos0[s] + 1, per = (ctx + p.splits - 1) / p.splits;
-  const int k_lo = j * per, k_hi = min(ctx, k_lo + per);
+  int k_lo, k_hi;
+  decode_split(rg.pos0[s] + 1, p.window, j, p.splits, &k_lo, &k_hi);
   const int vpr = W / 8;   // 16-byte vectors per row
   const __nv_bfloat16* cache = (const __nv_bfloat16*)p.cache;
   auto load_tile = [&](int k0, int buf) {

@@ -6,13 +6,16 @@
 //   postnorm_residual_kernel  x += mult * norm(s1 y1 + s2 y2): the norm sits on a sublayer's OUTPUT (serial blocks)
 //   glu_act_kernel            y = act(g) * u, act = gelu_tanh | silu
 //   bias_act_kernel           y = act(z + b), act = relu^2 | gelu_tanh | silu     (feed-forward without a gate)
+//   act_cols_kernel           the same without a bias on rows of any leading dimension (experts without a gate)
+//   polynorm_kernel           y = k1 u1 + k2 u2 + k3 u3 + k0, u_p = z^p / rms(z^p) over the row (feed-forward without a gate)
 //   token_shift_kernel        RWKV token shift: S mixes h + (h_prev - h) * mu_s, h_prev carried in the state slot
 //   head_rmsnorm_gate_kernel  per-head unit RMS, times a channel weight, times silu / sigmoid of a gate pre-activation
 //   clamped_glu_kernel        y = g * sigmoid(1.702 g) * (u + 1) with g = min(g, lim), u = clamp(u, -lim, lim)
 //   unary_kernel              tanh (decay low-rank bottleneck)
-//   block_combine_kernel      parallel block: x += ls1 * mixer + ls2 * (sum_k w_k expert_k + sigmoid(sg) * shared + b);
-//                             ls1, ls2, sg, b are optional (1, 1, no gate, 0); an identity expert's output is the
-//                             feed-forward's input row itself
+//   block_combine_kernel      parallel block: x += ls1 * g1 * mixer + ls2 * g2 * (sum_k w_k expert_k + sigmoid(sg) * shared + b);
+//                             ls1, ls2, sg, b are optional (1, 1, no gate, 0), and so are the per-token, per-channel residual
+//                             gates g = sigmoid(pre-activation + bias); an identity expert's output is the feed-forward's
+//                             input row itself
 #pragma once
 #include "common.cuh"
 #include "linear.cuh"
@@ -114,6 +117,34 @@ __global__ void bias_act_kernel(const float* __restrict__ z, const T* __restrict
     st_f<T>(y + (size_t)r * ff + c, act_f<ACT>(z[(size_t)r * ff + c] + (b ? ld_f<T>(b + c) : 0.f)));
 }
 
+// z [rows, ldz] fp32 -> y [rows, ff] (T) = act(z); rows at and beyond *n_rows (optional, on the device) are skipped
+template <typename T, int ACT>
+__global__ void act_cols_kernel(const float* __restrict__ z, int ldz, T* __restrict__ y, int ff, const int* __restrict__ n_rows) {
+  const int r = blockIdx.x;
+  if (n_rows && r >= *n_rows) return;
+  for (int c = threadIdx.x; c < ff; c += blockDim.x) st_f<T>(y + (size_t)r * ff + c, act_f<ACT>(z[(size_t)r * ldz + c]));
+}
+
+// z [rows, ff] fp32, coef [4] (T) = k1, k2, k3, k0 -> y [rows, ff] (T) = k1 z / r1 + k2 z^2 / r2 + k3 z^3 / r3 + k0 with
+// r_p = sqrt(mean over the row of z^(2p) + eps): three unit-RMS powers of the row, all in fp32
+template <typename T>
+__global__ void polynorm_kernel(const float* __restrict__ z, const T* __restrict__ coef, T* __restrict__ y, int ff, float eps) {
+  __shared__ float red[33];
+  const float* zr = z + (size_t)blockIdx.x * ff;
+  float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  for (int c = threadIdx.x; c < ff; c += blockDim.x) {
+    const float v = zr[c], v2 = v * v;
+    s1 += v2; s2 = fmaf(v2, v2, s2); s3 = fmaf(v2 * v, v2 * v, s3);
+  }
+  s1 = block_sum(s1, red); s2 = block_sum(s2, red); s3 = block_sum(s3, red);
+  const float a = ld_f<T>(coef) / sqrtf(s1 / (float)ff + eps), b = ld_f<T>(coef + 1) / sqrtf(s2 / (float)ff + eps),
+              g = ld_f<T>(coef + 2) / sqrtf(s3 / (float)ff + eps), e = ld_f<T>(coef + 3);
+  for (int c = threadIdx.x; c < ff; c += blockDim.x) {
+    const float v = zr[c];
+    st_f<T>(y + (size_t)blockIdx.x * ff + c, fmaf(v, fmaf(v, fmaf(v, g, b), a), e));
+  }
+}
+
 // mixes[s][m][c] = h[m][c] + (prev[m][c] - h[m][c]) * mu[s][c]; prev of a portion's first row comes from the slot
 // (zero at position 0).  h_prev is NOT written here: the scan kernel of the same layer saves the portion's last row after
 // every row of this kernel has read the old one (stream order).
@@ -200,6 +231,9 @@ struct CombineArgs {
   const int* sel;        // [M * top] chosen router output; outputs >= n_real are identity experts (nullptr: there are none)
   int n_real;
   const void* fin;       // [M, width] T the feed-forward's input (what an identity expert returns)
+  const float* gz;       // [M, ld_gz] pre-activations of the residual gates: mixer's in columns [0, width), feed-forward's in
+  int ld_gz;             //   [width, 2 width); nullptr: no gates
+  const void* gz_bias;   // [2 width] T
 };
 template <typename T>
 __global__ void block_combine_kernel(const CombineArgs p) {
@@ -208,6 +242,7 @@ __global__ void block_combine_kernel(const CombineArgs p) {
   for (int c = threadIdx.x; c < p.width; c += blockDim.x) {
     float y = p.mix[(size_t)m * p.width + c];
     if (p.ls1) y *= ld_f<T>((const T*)p.ls1 + c);
+    if (p.gz) y *= sigmoid_f(p.gz[(size_t)m * p.ld_gz + c] + ld_f<T>((const T*)p.gz_bias + c));
     if (p.routed || p.shared) {
       float f = 0.f;
       if (p.routed)
@@ -219,6 +254,7 @@ __global__ void block_combine_kernel(const CombineArgs p) {
         }
       if (p.shared) f = fmaf(sgate, p.shared[(size_t)m * p.width + c], f);
       if (p.ff_bias) f += ld_f<T>((const T*)p.ff_bias + c);
+      if (p.gz) f *= sigmoid_f(p.gz[(size_t)m * p.ld_gz + p.width + c] + ld_f<T>((const T*)p.gz_bias + p.width + c));
       y = p.ls2 ? fmaf(ld_f<T>((const T*)p.ls2 + c), f, y) : y + f;
     }
     p.x[(size_t)m * p.width + c] += y;

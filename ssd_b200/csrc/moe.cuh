@@ -1,7 +1,7 @@
 // moe.cuh — routing of a group-limited mixture of experts.
 //
 //   group_topk_router_kernel  one warp per token, all fp32.  scores = sigmoid(logits) or softmax(logits) over all E
-//       router outputs.  The CHOICE is made on choice scores = scores (+ a per-output selection bias): the outputs form
+//       router outputs, or the logits themselves with a softmax over the chosen ones as weights.  The CHOICE is made on choice scores = scores (+ a per-output selection bias): the outputs form
 //       `groups` equal, contiguous groups; a group scores the sum of its `group_best` (1 or 2) best choice scores; only
 //       outputs of the `keep` best groups compete (the others are shut out whatever their sign); the `top` best of
 //       those are chosen.  The WEIGHTS are the chosen outputs' plain scores (without the bias), optionally divided by
@@ -25,7 +25,8 @@ struct RouterArgs {
   int* sel;         // [M, top]
   float* wts;       // [M, top]
   int M, E, top, groups, keep;
-  int softmax;      // 0: sigmoid scores, 1: softmax over the E outputs
+  int softmax;      // 0: sigmoid scores, 1: softmax over the E outputs, 2: the raw logits choose and the weights are the
+                    //    softmax over the CHOSEN logits only (renorm is then implied)
   int group_best;   // 1 or 2
   int renorm;
   float route_scale;
@@ -48,7 +49,9 @@ __global__ void __launch_bounds__(kRouterWarps * 32) group_topk_router_kernel(co
   unsigned char* kept = s_kept[warp];
   const int E = p.E, G = p.groups, per = E / G;
   const float* z = p.z + (size_t)m * E;
-  if (p.softmax) {
+  if (p.softmax == 2) {
+    for (int e = lane; e < E; e += 32) sc[e] = z[e];
+  } else if (p.softmax) {
     float mx = -INFINITY;
     for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
     mx = warp_max(mx);
@@ -85,7 +88,7 @@ __global__ void __launch_bounds__(kRouterWarps * 32) group_topk_router_kernel(co
   for (int e = lane; e < E; e += 32)
     if (!kept[e / per]) ch[e] = -INFINITY;
   __syncwarp();
-  float mine = 0.f, total = 0.f;   // lane r keeps the r-th chosen score (top <= 32)
+  float mine = 0.f, total = 0.f, first = 0.f;   // lane r keeps the r-th chosen score (top <= 32)
   int mine_i = 0;
   for (int r = 0; r < p.top; ++r) {
     ArgMax a{-INFINITY, 0x7fffffff};
@@ -95,13 +98,17 @@ __global__ void __launch_bounds__(kRouterWarps * 32) group_topk_router_kernel(co
     __syncwarp();
     if (lane == 0) ch[a.i] = -INFINITY;
     __syncwarp();
-    const float w = sc[a.i];
+    float w = sc[a.i];
+    if (p.softmax == 2) {   // the first chosen logit is the largest: exponentials relative to it
+      if (r == 0) first = w;
+      w = expf(w - first);
+    }
     if (lane == r) { mine = w; mine_i = a.i; }
     total += w;
   }
   if (lane < p.top) {
     p.sel[(size_t)m * p.top + lane] = mine_i;
-    p.wts[(size_t)m * p.top + lane] = (p.renorm ? mine / (total + 1e-20f) : mine) * p.route_scale;
+    p.wts[(size_t)m * p.top + lane] = ((p.renorm || p.softmax == 2) ? mine / (total + 1e-20f) : mine) * p.route_scale;
   }
 }
 

@@ -1,4 +1,4 @@
-"""Layered ("hybrid") models: a program of layers, each one token mixer + an optional feed-forward.  Three designs are
+"""Layered ("hybrid") models: a program of layers, each one token mixer + an optional feed-forward.  Four designs are
 served through this module, told apart by config.json's `"architecture"`:
 
     Pikavik   parallel pre-norm blocks (mixer and mixture-of-experts feed-forward read the same normed input, unit-offset
@@ -12,6 +12,13 @@ served through this module, told apart by config.json's `"architecture"`:
               softmax, a sigmoid output gate and layers that read another layer's latent cache (`kv_from`);
               feed-forward dense (squared relu, biases) or a mixture of silu-GLU experts behind a softmax router
               with a selection bias, group limits, identity experts and an ungated shared expert
+    Kokatar   parallel blocks with ONE norm: mixer and feed-forward each read h + conv(h) (a short causal convolution
+              over time of the normed rows, taps of their own) and each result is multiplied by sigmoid(W_g h + b) before
+              it joins the residual; mixers `attention` (grouped-query, biased q | k | v behind a short convolution,
+              rotate-half rotation of the first dims, sliding window, a learned sink logit per head) and latent attention
+              without positions (sliding window, plain softmax); feed-forward dense with a PolyNorm activation or a
+              mixture of squared-relu experts whose weights are the softmax over the chosen logits, plus a gated shared
+              expert
 
     HybridSpec     what config.json (and, for sizes it does not list, the checkpoint's tensor shapes) says
     load_hybrid_weights   safetensors -> device tensors in the packed layout libssdk's ssdk_hyb_bind expects
@@ -34,7 +41,7 @@ import torch
 from . import lib as L
 
 MIXERS = {"wkv": L.MIX_WKV, "mlstm": L.MIX_MLSTM, "latent_attention": L.MIX_LATENT_ATTN, "rglru": L.MIX_RGLRU,
-          "mamba1": L.MIX_SELECTIVE, "parallel": L.MIX_ATTN_DELTA}
+          "mamba1": L.MIX_SELECTIVE, "parallel": L.MIX_ATTN_DELTA, "attention": L.MIX_ATTENTION}
 # which mixers and feed-forwards a design may list, and how its blocks join the residual stream
 DESIGNS = {
     "Pikavik": {"mixers": ("wkv", "mlstm", "latent_attention"), "mlp": ("moe",), "block": L.BLOCK_PARALLEL_PRENORM,
@@ -48,6 +55,12 @@ DESIGNS = {
                 "moe": {"route_softmax": 1, "route_bias": 1, "group_best": 1, "route_renorm": 0, "expert_act": L.ACT_SILU,
                         "shared_gate": 0},
                 "ffn": {"ff_act": L.ACT_RELU2}},
+    "Kokatar": {"mixers": ("attention", "latent_attention"), "mlp": ("dense", "moe"), "block": L.BLOCK_PARALLEL_ONE_NORM,
+                "norm_offset": 0.0, "dense": "ffn", "gated_residual": True,
+                "attention": {"rot_half": 1, "learned_sink": 1},
+                "latent": {"rot_interleaved": 0, "out_gate": 0, "learned_sink": 0},
+                "moe": {"route_top_softmax": 1, "group_best": 1, "expert_act": L.ACT_RELU2, "expert_glu": 0, "shared_gate": 1},
+                "ffn": {"ff_act": L.ACT_POLYNORM}},
 }
 RGLRU_DECAY_MULT = 8.0  # log a = -8 r softplus(lam)
 
@@ -114,6 +127,12 @@ class LayerSpec:
     expert_act: int = L.ACT_CLAMPED
     shared_gate: int = 1
     ff_act: int = L.ACT_RELU2
+    # attention window (0: none), pairing of the `attention` mixer's rotation, experts with or without a gate matrix,
+    # weights = softmax over the chosen logits
+    window: int = 0
+    rot_half: int = 0
+    expert_glu: int = 1
+    route_top_softmax: int = 0
 
     def cfg(self) -> L.HybLayerCfg:
         mlp = {"moe": L.MLP_MOE, "dense": L.MLP_GLU, "ffn": L.MLP_FFN, None: L.MLP_NONE}[self.mlp]
@@ -126,7 +145,8 @@ class LayerSpec:
                              self.d_heads, self.d_kv_heads, self.d_dim, self.d_vdim, self.left_scale, self.right_scale,
                              self.rot_interleaved, self.kv_from, self.out_gate, self.learned_sink, self.identity,
                              self.route_softmax, self.route_bias, self.group_best, self.route_renorm, self.expert_act,
-                             self.shared_gate, self.ff_act)
+                             self.shared_gate, self.ff_act, self.window, self.rot_half, self.expert_glu,
+                             self.route_top_softmax)
 
 
 @dataclass
@@ -138,6 +158,11 @@ class HybridSpec:
     architecture: str = "Pikavik"
     embed_scale: float = 1.0
     residual_mult: float = 1.0
+    canon_taps: int = 0       # one-norm blocks: taps of the sublayers' input convolutions (0: none)
+
+    @property
+    def gated_residual(self) -> bool:
+        return bool(DESIGNS[self.architecture].get("gated_residual"))
 
     @property
     def block(self) -> int:
@@ -154,13 +179,13 @@ class HybridSpec:
     @property
     def has_cache(self) -> bool:
         """Some layer keeps per-token rows in the paged cache (latent or grouped-query attention)."""
-        return any(l.mixer in ("latent_attention", "parallel") for l in self.layers)
+        return any(l.mixer in ("latent_attention", "parallel", "attention") for l in self.layers)
 
     has_latent = has_cache
 
     @property
     def has_state(self) -> bool:
-        return any(l.mixer != "latent_attention" for l in self.layers)
+        return self.canon_taps > 1 or any(l.mixer != "latent_attention" for l in self.layers)
 
     @classmethod
     def from_config(cls, cfg: dict, shapes: dict[str, list[int]] | None = None) -> "HybridSpec":
@@ -193,6 +218,14 @@ class HybridSpec:
                                d_heads=int(d["heads"]), d_kv_heads=int(d["kv_heads"]), d_dim=int(d["dim"]),
                                d_vdim=int(d["vdim"]), conv=int(d["conv"]), left_scale=float(m["left_scale"]),
                                right_scale=float(m["right_scale"]))
+            elif kind == "attention":
+                rot = m.get("rot") or {}
+                ls = LayerSpec(mixer=kind, heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]),
+                               vdim=int(m.get("vdim", m["dim"])), attn_scale=float(m["scale"]), conv=int(m.get("conv") or 1),
+                               rot_dims=int(rot.get("dims", 0)), rot_base=float(rot.get("base", 10000.0)),
+                               window=int((m.get("mask") or {}).get("size", 0)))
+                for key, val in (design.get("attention") or {}).items():
+                    setattr(ls, key, val)
             else:
                 ls = LayerSpec(mixer=kind, heads=int(m["heads"]), dim=int(m["dim"]))
             if kind == "wkv":
@@ -207,7 +240,8 @@ class HybridSpec:
                 ls.vdim, ls.gate_cap = int(m["vdim"]), float(m["gate_cap"])
             elif kind == "latent_attention":
                 rot = m.get("rot") or {}
-                ls.vdim, ls.rot_dim = int(m["vdim"]), int(m["rot_dim"])
+                ls.vdim, ls.rot_dim = int(m["vdim"]), int(m.get("rot_dim", 0))
+                ls.window = int((m.get("mask") or {}).get("size", 0))
                 ls.rot_dims, ls.rot_base = int(rot.get("dims", ls.rot_dim)), float(rot.get("base", 10000.0))
                 ls.kv_rank, ls.q_rank, ls.attn_scale = int(m["kv_rank"]), int(m.get("q_rank", 0)), float(m["scale"])
                 src = m.get("kv_from")
@@ -237,7 +271,8 @@ class HybridSpec:
             layers.append(ls)
         return cls(width=int(cfg["width"]), vocab=int(cfg["vocab"]), eps=float(cfg["norm"]["eps"]), layers=layers,
                    architecture=arch, embed_scale=float((cfg.get("embedding") or {}).get("scale", 1.0)),
-                   residual_mult=float(cfg.get("residual_mult", 1.0)))
+                   residual_mult=float(cfg.get("residual_mult", 1.0)),
+                   canon_taps=int((cfg.get("canon") or {}).get("taps", 0)) if design["block"] == L.BLOCK_PARALLEL_ONE_NORM else 0)
 
     @classmethod
     def from_dir(cls, path: str) -> "HybridSpec":
@@ -287,12 +322,21 @@ def pack_hybrid_weights(spec: HybridSpec, raw: dict[str, torch.Tensor], dtype: t
     w = {"EMBED": dev(t("embed")), "FINAL_NORM": dev(t("final.norm")), "layers": []}
     w["HEAD"] = w["EMBED"] if spec.tied_head else dev(t("head"))   # a tied head reads the table itself (without its scale)
     two_norms = spec.block == L.BLOCK_PARALLEL_TWO_NORMS
+    one_norm = spec.block == L.BLOCK_PARALLEL_ONE_NORM
+    scales = not two_norms and not one_norm
     for i, ls in enumerate(spec.layers):
         p, mx = f"l{i}.", f"l{i}.mix."
         lw = {"NORM": dev(t(p + "norm1"))}
+        if one_norm:   # per sublayer: taps of its input convolution, rows and bias of its residual gate
+            subs = ("1", "2") if ls.mlp else ("1",)
+            if spec.canon_taps > 0:
+                lw["CANON_W"] = dev(torch.stack([t(p + "canon" + k) for k in subs]))
+            if spec.gated_residual:
+                lw["RES_GATE"] = dev(torch.cat([t(p + "rg" + k) for k in subs]))
+                lw["RES_GATE_B"] = dev(torch.cat([t(p + "rg" + k + ".b") for k in subs]))
         if ls.mixer in ("wkv", "mlstm", "latent_attention"):
             lw["MIX_OUT"] = dev(t(mx + "o"))
-            if not two_norms:
+            if scales:
                 lw["LS_MIX"] = dev(t(p + "ls1"))
         if two_norms and ls.mlp:
             lw["NORM2"] = dev(t(p + "norm2"))
@@ -315,6 +359,17 @@ def pack_hybrid_weights(spec: HybridSpec, raw: dict[str, torch.Tensor], dtype: t
             lw["CONV_W"] = dev(torch.cat([t(d + "q.conv"), t(d + "k.conv"), t(d + "v.conv")]))
             lw["DELTA_ALOG"], lw["DELTA_DT_B"] = dev(t(d + "A_log")), dev(t(d + "dt_bias"))
             lw["MIX_NORM"] = dev(t(d + "norm").repeat(ls.d_heads))  # one weight per value channel, the same for every head
+        elif ls.mixer == "attention":
+            lw["ATTN_IN"] = dev(torch.cat([t(mx + "q"), t(mx + "k"), t(mx + "v")]))
+            if mx + "q.b" in raw:
+                lw["ATTN_IN_B"] = dev(torch.cat([t(mx + "q.b"), t(mx + "k.b"), t(mx + "v.b")]))
+            if mx + "q.conv" in raw:
+                lw["CONV_W"] = dev(torch.cat([t(mx + "q.conv"), t(mx + "k.conv"), t(mx + "v.conv")]))
+            else:   # no convolution: one tap of weight 1
+                lw["CONV_W"] = dev(torch.ones(lw["ATTN_IN"].shape[0], 1))
+            if ls.learned_sink:
+                lw["ATTN_SINK"] = dev(t(mx + "sink"))
+            lw["MIX_OUT"] = dev(t(mx + "o"))
         elif ls.mixer == "wkv":
             lw["WKV_MU"] = dev(torch.stack([t(mx + "mu." + s) for s in "rkvgw"]))
             for s in "rkvg":
@@ -339,8 +394,13 @@ def pack_hybrid_weights(spec: HybridSpec, raw: dict[str, torch.Tensor], dtype: t
             lw["LAT_UKT"] = dev(t(mx + "uk").view(ls.heads, ls.dim, ls.kv_rank).transpose(1, 2))
         if ls.mlp == "ffn":
             q = p + "mlp."
-            lw["FFN_IN"], lw["FFN_IN_B"] = dev(t(q + "up")), dev(t(q + "up.b"))
-            lw["FFN_OUT"], lw["FFN_OUT_B"] = dev(t(q + "down")), dev(t(q + "down.b"))
+            lw["FFN_IN"], lw["FFN_OUT"] = dev(t(q + "up")), dev(t(q + "down"))
+            if q + "up.b" in raw:
+                lw["FFN_IN_B"] = dev(t(q + "up.b"))
+            if q + "down.b" in raw:
+                lw["FFN_OUT_B"] = dev(t(q + "down.b"))
+            if ls.ff_act == L.ACT_POLYNORM:
+                lw["FFN_ACT"] = dev(t(q + "act"))
         if ls.mlp == "dense":
             q = p + "mlp."
             lw["NORM2"] = dev(t(p + "norm2"))
@@ -348,14 +408,15 @@ def pack_hybrid_weights(spec: HybridSpec, raw: dict[str, torch.Tensor], dtype: t
         if ls.mlp == "moe":
             q = p + "mlp."
             lw["ROUTER"] = dev(t(q + "router"))
-            if not two_norms:
+            if scales:
                 lw["LS_MLP"] = dev(t(p + "ls2"))
             if ls.route_bias:
                 lw["ROUTER_BIAS"] = dev(t(q + "correction"))
-            lw["EXPERT_IN"] = dev(torch.stack([torch.cat([t(f"{q}e{e}.gate"), t(f"{q}e{e}.up")]) for e in range(ls.experts)]))
+            mats = ("gate", "up") if ls.expert_glu else ("up",)   # an expert's input matrices, stacked by rows
+            lw["EXPERT_IN"] = dev(torch.stack([torch.cat([t(f"{q}e{e}.{k}") for k in mats]) for e in range(ls.experts)]))
             lw["EXPERT_OUT"] = dev(torch.stack([t(f"{q}e{e}.down") for e in range(ls.experts)]))
             if ls.shared_ff:
-                lw["SHARED_IN"] = dev(torch.cat([t(q + "shared.gate"), t(q + "shared.up")] +
+                lw["SHARED_IN"] = dev(torch.cat([t(q + "shared." + k) for k in mats] +
                                                 ([t(q + "shared.sg").reshape(1, -1)] if ls.shared_gate else [])))
                 lw["SHARED_OUT"] = dev(t(q + "shared.down"))
         w["layers"].append(lw)
@@ -496,7 +557,7 @@ class HybridRunner:
         self.max_logit_rows = max_logit_rows or max(1, min(max_tokens, (1 << 30) // spec.vocab))
         cfg = L.HybCfg(spec.width, spec.vocab, len(spec.layers), L.DT_BF16 if self.dtype == torch.bfloat16 else L.DT_F32,
                        spec.eps, max_tokens, max_seqs, self.max_logit_rows, block_size, self.max_blocks, spec.block, spec.norm_offset,
-                       spec.embed_scale, spec.residual_mult)
+                       spec.embed_scale, spec.residual_mult, spec.canon_taps, int(spec.gated_residual))
         layer_cfgs = (L.HybLayerCfg * len(spec.layers))(*[l.cfg() for l in spec.layers])
         h = C.c_void_p()
         L.check(self.lib.ssdk_hyb_create(C.byref(cfg), layer_cfgs, C.byref(h)), "ssdk_hyb_create")

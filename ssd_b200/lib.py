@@ -57,6 +57,7 @@ class HybLayerCfg(C.Structure):
         ("rot_interleaved", C.c_int32), ("kv_from", C.c_int32), ("out_gate", C.c_int32), ("learned_sink", C.c_int32),
         ("identity", C.c_int32), ("route_softmax", C.c_int32), ("route_bias", C.c_int32), ("group_best", C.c_int32),
         ("route_renorm", C.c_int32), ("expert_act", C.c_int32), ("shared_gate", C.c_int32), ("ff_act", C.c_int32),
+        ("window", C.c_int32), ("rot_half", C.c_int32), ("expert_glu", C.c_int32), ("route_top_softmax", C.c_int32),
     ]
 
 
@@ -67,21 +68,22 @@ class HybCfg(C.Structure):
         ("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("dtype", C.c_int32), ("eps", C.c_float),
         ("max_tokens", C.c_int32), ("max_seqs", C.c_int32), ("max_logit_rows", C.c_int32), ("block_size", C.c_int32),
         ("max_blocks_per_seq", C.c_int32), ("block", C.c_int32), ("norm_offset", C.c_float), ("embed_scale", C.c_float),
-        ("residual_mult", C.c_float),
+        ("residual_mult", C.c_float), ("canon_taps", C.c_int32), ("gated_residual", C.c_int32),
     ]
 
 
 # hybrid-model enums (include/ssdk.h)
 DT_F32, DT_BF16 = 0, 1
-MIX_WKV, MIX_MLSTM, MIX_LATENT_ATTN, MIX_RGLRU, MIX_SELECTIVE, MIX_ATTN_DELTA = 0, 1, 2, 3, 4, 5
+MIX_WKV, MIX_MLSTM, MIX_LATENT_ATTN, MIX_RGLRU, MIX_SELECTIVE, MIX_ATTN_DELTA, MIX_ATTENTION = 0, 1, 2, 3, 4, 5, 6
 MLP_NONE, MLP_MOE, MLP_GLU, MLP_FFN = 0, 1, 2, 3
-ACT_CLAMPED, ACT_SILU, ACT_GELU_TANH, ACT_RELU2 = 0, 1, 2, 3
-BLOCK_PARALLEL_PRENORM, BLOCK_SERIAL_POSTNORM, BLOCK_PARALLEL_TWO_NORMS = 0, 1, 2
+ACT_CLAMPED, ACT_SILU, ACT_GELU_TANH, ACT_RELU2, ACT_POLYNORM = 0, 1, 2, 3, 4
+BLOCK_PARALLEL_PRENORM, BLOCK_SERIAL_POSTNORM, BLOCK_PARALLEL_TWO_NORMS, BLOCK_PARALLEL_ONE_NORM = 0, 1, 2, 3
 HT_NAMES = ("EMBED HEAD FINAL_NORM NORM LS_MIX LS_MLP WKV_MU WKV_R WKV_K WKV_V WKV_G WKV_W1 WKV_W2 WKV_W0 WKV_U MLSTM_IN "
             "MLSTM_IB MLSTM_FB LAT_DOWN LAT_QNORM LAT_KVNORM LAT_UQ LAT_UKT LAT_UV LAT_SINK MIX_NORM MIX_OUT ROUTER "
             "EXPERT_IN EXPERT_OUT SHARED_IN SHARED_OUT NORM2 GLU_IN GLU_OUT CONV_W CONV_B RGLRU_IN RGLRU_IN_B RGLRU_GATE "
             "RGLRU_GATE_B RGLRU_LAM SEL_IN SEL_X SEL_DT SEL_DT_B SEL_ALOG SEL_D PAIR_IN ATTN_OUT DELTA_ALOG DELTA_DT_B "
-            "LAT_IN FFN_IN FFN_IN_B FFN_OUT FFN_OUT_B ROUTER_BIAS").split()
+            "LAT_IN FFN_IN FFN_IN_B FFN_OUT FFN_OUT_B ROUTER_BIAS ATTN_IN ATTN_IN_B ATTN_SINK FFN_ACT CANON_W RES_GATE "
+            "RES_GATE_B").split()
 HT = {n: i for i, n in enumerate(HT_NAMES)}
 
 # weight kinds (enum in include/ssdk.h)
