@@ -3,7 +3,7 @@ ssd/config.py + llm_engine.py:51-57 decide between Llama and Qwen3 (by `model_ty
 ("hybrid") family, whose config.json carries an `architecture` name and a list of layers instead of HF fields.
 
     dense   Llama / Qwen3 decoders: PairRunner + the speculative engine of libssdk (ssdk_spec_step, ssdk_forward_tokens)
-    hybrid  Pikavik, Kefurax, Lisenex (layered designs): HybridRunner + the ragged forward of libssdk (ssdk_hyb_forward)
+    hybrid  Pikavik, Kefurax, Lisenex, Kokatar (layered designs): HybridRunner + the ragged forward of libssdk (ssdk_hyb_forward)
 """
 from __future__ import annotations
 
@@ -22,6 +22,7 @@ FAMILIES: list[Family] = [
     Family("pikavik", "hybrid", lambda d: d.get("architecture") == "Pikavik"),
     Family("kefurax", "hybrid", lambda d: d.get("architecture") == "Kefurax"),
     Family("lisenex", "hybrid", lambda d: d.get("architecture") == "Lisenex"),
+    Family("kokatar", "hybrid", lambda d: d.get("architecture") == "Kokatar"),
     Family("qwen3", "dense", lambda d: "qwen3" in str(d.get("model_type", "")).lower()),
     Family("llama", "dense", lambda d: "hidden_size" in d),
 ]
