@@ -464,9 +464,10 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     # hybrid family (ssd_b200/hybrid_bench.py); the default workload and its JSON line are unaffected
-    ap.add_argument("--arch", default="pair", choices=["pair", "pikavik", "kefurax", "lisenex"],
+    ap.add_argument("--arch", default="pair", choices=["pair", "pikavik", "kefurax", "lisenex", "kokatar"],
                     help="pikavik: prefill / decode throughput of the hybrid family beside a Llama stack of equal size; "
-                         "kefurax / lisenex: the same for a Kefurax / Lisenex stack beside a Pikavik stack of equal size")
+                         "kefurax / lisenex: the same for a Kefurax / Lisenex stack beside a Pikavik stack of equal size; "
+                         "kokatar: a Kokatar stack beside a Lisenex stack of equal size")
     ap.add_argument("--hybrid-size", default="all", choices=["all", "s", "m"])
     ap.add_argument("--prompt-len-hybrid", type=int, default=2048)
     ap.add_argument("--hybrid-batch", type=int, default=8)
@@ -474,7 +475,7 @@ def main():
     ap.add_argument("--no-dense-arm", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.arch in ("pikavik", "kefurax", "lisenex"):
+    if args.arch in ("pikavik", "kefurax", "lisenex", "kokatar"):
         from ssd_b200.hybrid_bench import run as run_hybrid
         print(json.dumps(run_hybrid(args)), flush=True)
         return

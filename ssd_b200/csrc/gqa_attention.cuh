@@ -104,36 +104,6 @@ constexpr int kGqaDecWarps = 4;
 
 inline size_t gqa_decode_smem(int D, int V) { return ((size_t)(D + 3) / 4 * 4 + (size_t)kGqaDecWarps * (V + 2)) * 4; }
 
-// N contiguous elements of storage type T -> floats, with the widest loads their size allows (the caller guarantees that
-// p is aligned to min(16, N * sizeof(T)) bytes)
-template <typename T, int N>
-SSDK_DEVINL void ld_contig(const T* p, float* f) {
-  constexpr int kBytes = N * (int)sizeof(T);
-  if constexpr (kBytes % 16 == 0) {
-    uint32_t w[kBytes / 4];
-#pragma unroll
-    for (int i = 0; i < kBytes / 16; ++i) {
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(p) + i);
-      w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
-    }
-#pragma unroll
-    for (int i = 0; i < N; ++i) {
-      if constexpr (sizeof(T) == 4) f[i] = __uint_as_float(w[i]);
-      else f[i] = __uint_as_float((i & 1) ? (w[i >> 1] & 0xffff0000u) : (w[i >> 1] << 16));
-    }
-  } else if constexpr (kBytes == 8) {
-    const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
-    if constexpr (sizeof(T) == 4) { f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); }
-    else { f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u); f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u); }
-  } else if constexpr (kBytes == 4 && sizeof(T) == 2) {
-    const uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(p));
-    f[0] = __uint_as_float(v << 16); f[1] = __uint_as_float(v & 0xffff0000u);
-  } else {
-#pragma unroll
-    for (int i = 0; i < N; ++i) f[i] = ld_f<T>(p + i);
-  }
-}
-
 // grid (n_seqs, H, splits), kGqaDecWarps warps.  A warp takes 32 keys at a time: first every lane scores ONE key (a
 // thread-local dot product over D, the key row read in 16-byte pieces where its alignment allows), then every lane owns
 // the VPL = ceil(V / 32) value columns lane VPL .. lane VPL + VPL - 1 (one vector load per key) and the 32 weights are

@@ -975,7 +975,15 @@ struct HybRun {
         ssdk::InputConvArgs ia;
         ia.h = e->h; ia.w = Lr.t[SSDK_HT_CANON_W].p; ia.y1 = e->hc; ia.y2 = has_ff ? e->h2 : nullptr;
         ia.hist = e->state + Lr.canon_off; ia.slot_stride = e->slot_floats; ia.C = W; ia.taps = taps;
-        CKI(L.go(ssdk::input_conv_kernel<T>, dim3(M, (W + 255) / 256), dim3(256), 0, ia, rg));
+        // 16 bytes of channels per thread when rows, taps and history rows start on 16-byte boundaries (2 .. 4 taps)
+        constexpr int kVec = 16 / (int)sizeof(T);
+        const bool vec = W % kVec == 0 && taps >= 2 && taps <= 4 && (((uintptr_t)ia.h | (uintptr_t)ia.w | (uintptr_t)ia.y1 | (uintptr_t)ia.y2) & 15) == 0 &&
+                         ((uintptr_t)ia.hist & 15) == 0 && e->slot_floats % 4 == 0 && W % 4 == 0;
+        const dim3 vgrid(M, (W / kVec + 127) / 128), vblock(128);
+        if (vec && taps == 4) CKI(L.go(ssdk::input_conv_vec_kernel<T, 4>, vgrid, vblock, 0, ia, rg));
+        else if (vec && taps == 3) CKI(L.go(ssdk::input_conv_vec_kernel<T, 3>, vgrid, vblock, 0, ia, rg));
+        else if (vec && taps == 2) CKI(L.go(ssdk::input_conv_vec_kernel<T, 2>, vgrid, vblock, 0, ia, rg));
+        else CKI(L.go(ssdk::input_conv_kernel<T>, dim3(M, (W + 255) / 256), dim3(256), 0, ia, rg));
         if (taps > 1) CKI(L.go(ssdk::input_conv_state_kernel<T>, dim3(rg.n_seqs, (W + 255) / 256), dim3(256), 0, ia, rg));
         hin = e->hc;
         fin = e->h2;

@@ -32,6 +32,55 @@ struct Ragged {
   int n_seqs, M, max_blocks, block_size;
 };
 
+// N contiguous elements of storage type T -> floats, with the widest loads their size allows (the caller guarantees that
+// p is aligned to min(16, N * sizeof(T)) bytes)
+template <typename T, int N>
+SSDK_DEVINL void ld_contig(const T* p, float* f) {
+  constexpr int kBytes = N * (int)sizeof(T);
+  if constexpr (kBytes % 16 == 0) {
+    uint32_t w[kBytes / 4];
+#pragma unroll
+    for (int i = 0; i < kBytes / 16; ++i) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(p) + i);
+      w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+    }
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      if constexpr (sizeof(T) == 4) f[i] = __uint_as_float(w[i]);
+      else f[i] = __uint_as_float((i & 1) ? (w[i >> 1] & 0xffff0000u) : (w[i >> 1] << 16));
+    }
+  } else if constexpr (kBytes == 8) {
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
+    if constexpr (sizeof(T) == 4) { f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); }
+    else { f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u); f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u); }
+  } else if constexpr (kBytes == 4 && sizeof(T) == 2) {
+    const uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(p));
+    f[0] = __uint_as_float(v << 16); f[1] = __uint_as_float(v & 0xffff0000u);
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) f[i] = ld_f<T>(p + i);
+  }
+}
+
+// N floats -> N contiguous elements of storage type T (p aligned to min(16, N * sizeof(T)) bytes, N * sizeof(T) a multiple of 16)
+template <typename T, int N>
+SSDK_DEVINL void st_contig(T* p, const float* f) {
+  constexpr int kBytes = N * (int)sizeof(T);
+  static_assert(kBytes % 16 == 0, "st_contig writes whole 16-byte pieces");
+  uint32_t w[kBytes / 4];
+#pragma unroll
+  for (int i = 0; i < kBytes / 4; ++i) {
+    if constexpr (sizeof(T) == 4) {
+      w[i] = __float_as_uint(f[i]);
+    } else {
+      const __nv_bfloat162 v = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&v);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kBytes / 16; ++i) reinterpret_cast<uint4*>(p)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+}
+
 template <typename T>
 __global__ void embed_rows_kernel(const int* __restrict__ ids, const T* __restrict__ embed, float* __restrict__ x, int width,
                                   int vocab, float scale, T* __restrict__ xt) {

@@ -446,6 +446,8 @@ def random_hybrid_weights(spec: HybridSpec, dtype: torch.dtype, device, seed: in
 
     if spec.block == L.BLOCK_SERIAL_POSTNORM:
         w["FINAL_NORM"] = vec(W, 1.0)
+    if spec.block == L.BLOCK_PARALLEL_ONE_NORM:
+        w["FINAL_NORM"] = vec(W, 1.0)
     if spec.block == L.BLOCK_PARALLEL_TWO_NORMS:
         w["FINAL_NORM"] = vec(W, 1.0)
         if spec.tied_head:   # the table is read as it is by the head: unit-size logits, the embedding's scale restores O(1) rows
@@ -453,6 +455,40 @@ def random_hybrid_weights(spec: HybridSpec, dtype: torch.dtype, device, seed: in
             w["HEAD"] = w["EMBED"]
     for ls in spec.layers:
         H, D, V = ls.heads, ls.dim, ls.vdim
+        if spec.block == L.BLOCK_PARALLEL_ONE_NORM:
+            subs = 2 if ls.mlp else 1
+            lw = {"NORM": vec(W, 1.0), "MIX_OUT": lin(W, H * V)}
+            if spec.canon_taps > 0:
+                lw["CANON_W"] = (torch.randn(subs, W, spec.canon_taps, generator=g, device=device) * 0.3).to(dtype)
+            if spec.gated_residual:
+                lw["RES_GATE"], lw["RES_GATE_B"] = lin(subs * W, W), vec(subs * W, 0.5, 0.5)
+            if ls.mixer == "attention":
+                n_in = H * D + ls.kv_heads * (D + V)
+                lw["ATTN_IN"], lw["ATTN_IN_B"] = lin(n_in, W), vec(n_in, 0.0, 0.3)
+                lw["CONV_W"] = (torch.randn(n_in, ls.conv, generator=g, device=device) * 0.5).to(dtype)
+                if ls.learned_sink:
+                    lw["ATTN_SINK"] = vec(H, 0.0, 1.0)
+            elif ls.mixer == "latent_attention" and not ls.q_rank and ls.kv_from < 0:
+                KR, R = ls.kv_rank, ls.rot_dim
+                lw["LAT_IN"], lw["LAT_KVNORM"] = lin(H * (D + R) + KR + R + (H * V if ls.out_gate else 0), W), vec(KR, 1.0)
+                lw["LAT_UV"], lw["LAT_UKT"] = lin(H * V, KR), (lin(H, KR, D) * (D / KR) ** 0.5).contiguous()
+                if ls.learned_sink:
+                    lw["LAT_SINK"] = vec(H, 0.0, 1.0)
+            else:
+                raise ValueError("random weights of one-norm blocks are made for attention and latent attention with full-rank queries")
+            mats = 2 if ls.expert_glu else 1
+            if ls.mlp == "ffn":
+                lw["FFN_IN"], lw["FFN_OUT"] = lin(ls.ff, W), lin(W, ls.ff)
+                if ls.ff_act == L.ACT_POLYNORM:
+                    lw["FFN_ACT"] = torch.tensor([0.6, 0.4, -0.3, 0.1], device=device).to(dtype)
+            elif ls.mlp == "moe":
+                lw["ROUTER"] = lin(ls.experts + ls.identity, W)
+                lw["EXPERT_IN"], lw["EXPERT_OUT"] = lin(ls.experts, mats * ls.ff, W), lin(ls.experts, W, ls.ff)
+                if ls.shared_ff:
+                    lw["SHARED_IN"] = lin(mats * ls.shared_ff + (1 if ls.shared_gate else 0), W)
+                    lw["SHARED_OUT"] = lin(W, ls.shared_ff)
+            w["layers"].append(lw)
+            continue
         if spec.block == L.BLOCK_PARALLEL_TWO_NORMS:
             if ls.mixer != "latent_attention" or ls.q_rank:
                 raise ValueError("random weights of two-norm blocks are made for latent attention with full-rank queries")

@@ -1,4 +1,4 @@
-"""Throughput of the hybrid families (bench.py --arch pikavik | kefurax | lisenex).
+"""Throughput of the hybrid families (bench.py --arch pikavik | kefurax | lisenex | kokatar).
 
 --arch pikavik: a Pikavik stack beside the closest dense model of the framework (below).
 --arch kefurax: a Kefurax stack (attention + delta-rule pair with a dense feed-forward, selective scan, rglru, ...) beside
@@ -6,6 +6,10 @@ the closest existing model of the framework, a Pikavik stack of the same width, 
 --arch lisenex: a Lisenex stack (latent attention with full-rank queries in every layer, every second layer reading the
 layer before's latent pool; a dense squared-relu feed-forward first, then softmax-routed experts with identity experts and a
 shared expert) beside the same Pikavik stack.
+--arch kokatar: a Kokatar stack (one-norm blocks with input convolutions and residual gates; windowed grouped-query
+attention with a learned sink and windowed latent attention without positions; a dense PolyNorm feed-forward or
+squared-relu experts with a gated shared expert) beside the closest existing model of the framework, a Lisenex stack of the
+same width, depth, vocabulary and feed-forward / expert sizes.
 
 For every size: a Pikavik stack (mLSTM, wkv, wkv, latent attention, ... each with a grouped mixture of experts and a
 shared expert) with random weights, and a Llama stack of the same width, depth and ACTIVE feed-forward size
@@ -86,6 +90,33 @@ def lisenex_spec(z):
                 setattr(ls, k, v)
         layers.append(ls)
     return HybridSpec(z["width"], z["vocab"], 1e-6, layers, architecture="Lisenex", embed_scale=float(z["width"]) ** 0.5)
+
+
+def kokatar_spec(z, window=1024):
+    """Layers that resemble a real model's: attention with 128-wide heads, four query heads per key/value head, half of a
+    head rotated, 4 taps on q | k | v; latent attention with 16 heads of 64 / 128 over a latent of 256 / 512; every layer
+    looks back `window` tokens; 4 taps on the sublayers' inputs; feed-forwards alternate between a dense one as wide as a
+    token's active experts and `experts` routed experts with a shared one."""
+    from .hybrid import DESIGNS, HybridSpec, LayerSpec
+    d = DESIGNS["Kokatar"]
+    W = z["width"]
+    heads = W // 128
+    layers = []
+    for i in range(z["layers"]):
+        if i % 3 == 0:
+            ls = LayerSpec("attention", heads, 128, 128, rot_dims=64, rot_base=10000.0, attn_scale=128 ** -0.5,
+                           kv_heads=max(1, heads // 4), conv=4, window=window, **d["attention"])
+        else:
+            ls = LayerSpec("latent_attention", z["lh"], z["ld"], z["ld"], kv_rank=z["kvr"], attn_scale=z["ld"] ** -0.5, window=window,
+                           **d["latent"])
+        if i % 2 == 0:
+            ls.mlp, ls.ff, ls.ff_act = "ffn", z["top"] * z["ff"] + z["sff"], d["ffn"]["ff_act"]
+        else:
+            ls.mlp, ls.experts, ls.top, ls.ff, ls.shared_ff = "moe", z["experts"], z["top"], z["ff"], z["sff"]
+            for k, v in d["moe"].items():
+                setattr(ls, k, v)
+        layers.append(ls)
+    return HybridSpec(W, z["vocab"], 1e-6, layers, architecture="Kokatar", canon_taps=4)
 
 
 def _events(fn, warmup, steps):
@@ -213,7 +244,28 @@ def run_lisenex(args):
     return out
 
 
+def run_kokatar(args):
+    out = {"metric": "prefill and decode tokens/s, Kokatar beside Lisenex at equal width / depth / feed-forward and expert sizes",
+           "dtype": "bf16", "data": "synthetic (random weights, random token ids)", "n_gpus": 1, "steps": args.steps,
+           "warmup": args.warmup, "timing": "CUDA events around the public forward call, median; every pass streams the stack's "
+           "weights (> 126 MB L2 for size m; size s partly L2-resident, stated here)", "sizes": {}}
+    names = [args.hybrid_size] if args.hybrid_size != "all" else list(SIZES)
+    for name in names:
+        z = SIZES[name]
+        row = {"config": {k: z[k] for k in ("width", "layers", "experts", "top", "ff", "sff", "vocab")}, "prompt": args.prompt_len_hybrid,
+               "decode_batch": args.hybrid_batch, "window": 1024}
+        row["kokatar"] = run_pikavik(z, args.prompt_len_hybrid, args.hybrid_batch, args.warmup, args.steps, spec_fn=kokatar_spec)
+        if not args.no_dense_arm:
+            row["lisenex"] = run_pikavik(z, args.prompt_len_hybrid, args.hybrid_batch, args.warmup, args.steps, spec_fn=lisenex_spec)
+        if args.hybrid_fp32:
+            row["kokatar_fp32"] = run_pikavik(z, args.prompt_len_hybrid, args.hybrid_batch, args.warmup, args.steps, "float32", kokatar_spec)
+        out["sizes"][name] = row
+    return out
+
+
 def run(args):
+    if getattr(args, "arch", "pikavik") == "kokatar":
+        return run_kokatar(args)
     if getattr(args, "arch", "pikavik") == "kefurax":
         return run_kefurax(args)
     if getattr(args, "arch", "pikavik") == "lisenex":
